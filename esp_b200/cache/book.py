@@ -5,7 +5,8 @@ Nothing here touches a device.  A *slot* is a sequence's handle for the time it
 lives; a *page* holds PAGE consecutive positions of one sequence (for every
 layer of its group).  Layers with the same needs form a group with a pool of
 its own: a group of full-attention layers keeps every position, a group of
-windowed layers gives pages back once the window has passed them.
+windowed layers gives pages back once the window has passed them, a group whose
+queries see their own block of positions only once the block is complete.
 """
 from __future__ import annotations
 
@@ -66,6 +67,11 @@ class KvLayout:
     window: Optional[int] = None     # None: keep every position
     values: bool = True              # False: one pool of rows only (a layer whose values are part of its key rows)
     value_dim: Optional[int] = None  # size of a value head where it differs from a key head's
+    chunk: Optional[int] = None      # C: a query sees the keys of its own block of C positions (counted from 0) only
+
+    @property
+    def keeps_all(self) -> bool:
+        return self.window is None and self.chunk is None
 
     @property
     def row_elements(self) -> int:
@@ -86,6 +92,8 @@ class GroupBook:
 
     def first_needed(self, length: int) -> int:
         """First position that a query at position ``length`` can still see."""
+        if self.layout.chunk is not None:
+            return length - length % self.layout.chunk
         if self.layout.window is None:
             return 0
         return max(0, length - self.layout.window + 1)
@@ -95,7 +103,7 @@ class GroupBook:
         needs and does not hold yet."""
         table = self.tables.get(slot, [])
         hi = pages_for(new_len)
-        if self.layout.window is None:
+        if self.layout.keeps_all:
             # nothing is ever given back before the slot closes: the table has no gaps
             return list(range(len(table), hi)) if hi > len(table) else []
         lo = self.first_needed(old_len) // PAGE
@@ -128,7 +136,7 @@ class GroupBook:
     def trim(self, slot: int, length: int) -> None:
         """Give back pages that no later query of the slot can see."""
         table = self.tables.get(slot)
-        if not table or self.layout.window is None:
+        if not table or self.layout.keeps_all:
             return
         keep_from = self.first_needed(length) // PAGE
         gone = [p for p in table[:keep_from] if p >= 0]

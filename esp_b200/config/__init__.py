@@ -5,8 +5,9 @@ from .registry import config_from_dict, config_from_json, register_architecture,
 from .qwen2_moe import Qwen2MoeConfig
 from .zusepel import ZusepelConfig
 from .vumedra import VumedraConfig
+from .migosun import MigosunConfig
 
 __all__ = ["AttentionSpec", "BlockSpec", "DecayBonusRecurrenceSpec", "DenseFfnSpec", "DepthMixBlockSpec",
            "LatentAttentionSpec", "LowerBoundRecurrenceSpec", "ModelPlan", "MoeFfnSpec", "NormSpec", "PositionSpec",
-           "ScaledRopeSpec", "ScheduleEntry", "XieluFfnSpec", "ZusepelConfig", "VumedraConfig", "config_from_dict", "config_from_json", "register_architecture",
+           "ScaledRopeSpec", "ScheduleEntry", "XieluFfnSpec", "ZusepelConfig", "VumedraConfig", "MigosunConfig", "config_from_dict", "config_from_json", "register_architecture",
            "supported_architectures", "Qwen2MoeConfig"]

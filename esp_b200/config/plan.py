@@ -381,6 +381,165 @@ class SandwichBlockSpec:
 
 
 @dataclass(frozen=True)
+class WideNormAttentionNames:
+    """Tensor names of an attention layer whose query and key norms span the whole projection, after the spec's prefix."""
+    q: str = "q"
+    k: str = "k"
+    v: str = "v"
+    o: str = "o"
+    q_norm: str = "q.norm"
+    k_norm: str = "k.norm"
+    sink: str = "sink"
+
+
+@dataclass(frozen=True)
+class WideNormAttentionSpec:
+    """Causal softmax attention over cached keys and values with grouped query heads, where the RMS norm of the
+    queries (and of the keys) runs over the whole projection, all heads at once, with a weight per channel, before the
+    rotation; the rotation (``position``, split-half pairs) covers the first channels of every head; scores are
+    multiplied by ``scale`` as given; keys and values may have different sizes.  Which keys a query sees: every
+    earlier one, the last ``window``, or (``chunk``) those of its own block of ``chunk`` positions counted from the
+    sequence's start.  ``learned_sink``: the softmax's denominator holds one more term exp(sink_h), a learned number
+    per head that is not scaled and carries no value."""
+    hidden: int
+    num_heads: int
+    num_kv_heads: int
+    key_dim: int
+    value_dim: int
+    scale: float
+    eps: float
+    learned_sink: bool
+    window: Optional[int]
+    chunk: Optional[int]
+    position: Optional[ScaledRopeSpec]
+    prefix: str
+    kind: str = "attention_widenorm"
+    names: WideNormAttentionNames = WideNormAttentionNames()
+
+
+@dataclass(frozen=True)
+class GatedDeltaNames:
+    q: str = "q"
+    k: str = "k"
+    v: str = "v"
+    o: str = "o"
+    conv: str = ".conv"              # after q, k or v
+    beta: str = "b"
+    decay_log: str = "A_log"
+    decay_in: str = "a1"
+    decay_out: str = "a2"
+    decay_bias: str = "dt_bias"
+    gate_in: str = "g1"
+    gate_out: str = "g2"
+    norm: str = "norm"
+
+
+@dataclass(frozen=True)
+class GatedDeltaSpec:
+    """Delta rule with a decay per head and key channel.  q, k (``num_kv_heads`` heads of ``key_dim``) and v
+    (``num_heads`` heads of ``value_dim``) pass a causal convolution of ``taps`` per channel and SiLU; q and k become unit
+    vectors per head (x / sqrt(sum x^2 + unit_eps)), q times key_dim^(-1/2);  beta = sigmoid(W_b h) per head;
+    d = exp(-exp(A_h) softplus(W_a2 W_a1 h + bias)) per head and key channel.  Per head, in this order:
+    S <- diag(d) S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q.  Each head's o is scaled to unit root mean
+    square (``eps``), times a weight per value channel shared by the heads, times sigmoid(W_g2 W_g1 h); then W_o.
+    Value head h reads query/key head h // (num_heads / num_kv_heads).  The two inner widths come from the tensors."""
+    hidden: int
+    num_heads: int
+    num_kv_heads: int
+    key_dim: int
+    value_dim: int
+    taps: int
+    decay_rank: int
+    gate_rank: int
+    eps: float
+    prefix: str
+    unit_eps: float = 1e-6
+    kind: str = "gated_delta"
+    names: GatedDeltaNames = GatedDeltaNames()
+
+
+@dataclass(frozen=True)
+class ChannelDecayAttentionNames:
+    q: str = "q"
+    k: str = "k"
+    v: str = "v"
+    o: str = "o"
+    gate: str = "g"
+    norm: str = "norm"
+    decay_in: str = "a1"
+    decay_out: str = "a2"
+    decay_bias: str = "a2.b"
+
+
+@dataclass(frozen=True)
+class ChannelDecayAttentionSpec:
+    """Gated linear attention: S_t = diag(a_t) S_(t-1) + k_t v_t^T, o_t = S_t^T q_t per head with q = W_q h
+    key_dim^(-1/2) and a_t = sigmoid(W_a2 W_a1 h + bias)^(1/tau) per head and key channel; every head's o is RMS-normed
+    with a weight per value channel shared by the heads, the heads' concatenation is multiplied by silu(W_g h),
+    then W_o.  The decay's inner width comes from the tensors."""
+    hidden: int
+    num_heads: int
+    key_dim: int
+    value_dim: int
+    tau: float
+    decay_rank: int
+    eps: float
+    prefix: str
+    kind: str = "gla"
+    names: ChannelDecayAttentionNames = ChannelDecayAttentionNames()
+
+
+@dataclass(frozen=True)
+class ParallelMixerSpec:
+    """Several mixers side by side on the same input; the result is sum_i scales[i] * branches[i](h)."""
+    hidden: int
+    branches: tuple                  # mixer specs
+    scales: tuple                    # one number per branch
+    kind: str = "parallel_sum"
+
+
+@dataclass(frozen=True)
+class ClampedGluFfnSpec:
+    """down(g sigmoid(alpha g) (u + up_shift)) with g = min(gate h, limit) and u = clamp(up h, -limit, limit)."""
+    hidden: int
+    intermediate: int
+    limit: float
+    prefix: str
+    alpha: float = 1.702
+    up_shift: float = 1.0
+    kind: str = "glu_clamped"
+    names: SwiGluNames = SwiGluNames("gate", "up", "down")
+
+
+@dataclass(frozen=True)
+class HyperConnectionNames:
+    """Tensor names of one sublayer's connection weights, after its prefix."""
+    read: str = "in"
+    write: str = "out"
+    mix: str = "mix"
+
+
+@dataclass(frozen=True)
+class HyperConnectionBlockSpec:
+    """A pre-norm layer over ``streams`` copies of the residual stream x_1 .. x_s (all equal to what enters the
+    stack).  A sublayer reads u = sum_s in[s] x_s, computes y = sublayer(norm(u)), and writes, all streams at once
+    from the old ones, x_t <- sum_s mix[s, t] x_s + out[t] y.  Behind the stack's last layer the streams are summed.
+    ``index`` counts the layers of the stack from 0, ``depth`` is their number."""
+    mixer: Any
+    ffn: Any                         # None: the layer has a mixer only
+    mixer_norm: NormSpec
+    ffn_norm: Optional[NormSpec]
+    streams: int
+    mixer_prefix: str                # e.g. "l3.hc1."
+    ffn_prefix: Optional[str]
+    index: int
+    depth: int
+    hidden: int
+    kind: str = "hyper_connections"
+    names: HyperConnectionNames = HyperConnectionNames()
+
+
+@dataclass(frozen=True)
 class BlockSpec:
     """One layer: which parts it has and how they are arranged."""
     mixer: Any                       # any spec object with a ``kind``

@@ -3,9 +3,10 @@
 // prefill and decode alike and any head size up to 256.
 //
 // The query at absolute position a sees key j iff j <= a and (window == 0 or
-// a - j < window).  score = dot(q, k_j) / sqrt(hd) (divided after the product), or dot(q, k_j) * scale when a scale is
+// a - j < window), or, with ``chunk`` > 0, iff j <= a and both lie in the same block of ``chunk`` positions.  score = dot(q, k_j) / sqrt(hd) (divided after the product), or dot(q, k_j) * scale when a scale is
 // given.  Values may have another size than keys (vd).  With ``sink`` the denominator holds one more term, exp(0 - max):
-// a key of score zero that carries no value.
+// a key of score zero that carries no value; with ``sink_vals`` the term is exp(sink_vals[head] - max), a number per head
+// that is not scaled.
 // Keys are walked in chunks of CHUNK positions aligned to absolute multiples of
 // CHUNK with a running maximum and sum, so the order of every addition depends
 // on the query's position alone: not on how the sequence was cut into steps,
@@ -22,7 +23,8 @@ __global__ void __launch_bounds__(THREADS)
 attn_simt_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T* __restrict__ v_cache,
                  T* __restrict__ out, const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
                  const int* __restrict__ block_table, int table_stride, int n_pages, int page, int nh, int nkv, int hd,
-                 int vd, float scale, int sink, int window, int* __restrict__ status) {
+                 int vd, float scale, int sink, const float* __restrict__ sink_vals, int window, int chunk,
+                 int* __restrict__ status) {
     __shared__ float qs[MAX_HD];
     __shared__ float ps[CHUNK];
     __shared__ int pages[CHUNK];      // page id of each key of the chunk (or -1)
@@ -30,12 +32,12 @@ attn_simt_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T
     const int n = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
     const int seq = tok_seq[n], pos = tok_pos[n];
     const int kvh = h / (nh / nkv);
-    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    const int lo = first_visible_key(pos, window, chunk);
     const T* qrow = q + ((size_t)n * nh + h) * hd;
     for (int d = tid; d < hd; d += THREADS) qs[d] = to_f32(qrow[d]);
     const float root = sqrtf((float)hd);
-    // the sink is a key of score zero ahead of all others: the running maximum and sum start from it
-    float m_run = sink ? 0.f : -INFINITY, l_run = sink ? 1.f : 0.f;
+    // the sink is a key of score zero (or of the head's own score) ahead of all others: the running maximum and sum start from it
+    float m_run = sink ? (sink_vals ? sink_vals[h] : 0.f) : -INFINITY, l_run = sink ? 1.f : 0.f;
     float acc[MAX_HD / THREADS];
 #pragma unroll
     for (int i = 0; i < MAX_HD / THREADS; i++) acc[i] = 0.f;
@@ -104,8 +106,8 @@ attn_simt_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T
 
 ESP_API int esp_attn_simt(const void* q, const void* k_cache, const void* v_cache, void* out, int is_bf16,
                           const int* tok_seq, const int* tok_pos, const int* block_table, int table_stride, int n_pages,
-                          int page, int n_tokens, int nh, int nkv, int hd, int vd, float scale, int sink, int window,
-                          int* status, cudaStream_t stream) {
+                          int page, int n_tokens, int nh, int nkv, int hd, int vd, float scale, int sink,
+                          const float* sink_vals, int window, int chunk, int* status, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (vd <= 0) vd = hd;
     if (vd > MAX_HD || hd > MAX_HD || hd <= 0 || nkv <= 0 || nh % nkv != 0 || nh > 65535) return (int)cudaErrorInvalidValue;
@@ -113,11 +115,11 @@ ESP_API int esp_attn_simt(const void* q, const void* k_cache, const void* v_cach
     if (is_bf16)
         attn_simt_kernel<bf16><<<grid, THREADS, 0, stream>>>((const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache,
                                                             (bf16*)out, tok_seq, tok_pos, block_table, table_stride,
-                                                            n_pages, page, nh, nkv, hd, vd, scale, sink, window, status);
+                                                            n_pages, page, nh, nkv, hd, vd, scale, sink, sink_vals, window, chunk, status);
     else
         attn_simt_kernel<float><<<grid, THREADS, 0, stream>>>((const float*)q, (const float*)k_cache,
                                                              (const float*)v_cache, (float*)out, tok_seq, tok_pos,
                                                              block_table, table_stride, n_pages, page, nh, nkv, hd,
-                                                             vd, scale, sink, window, status);
+                                                             vd, scale, sink, sink_vals, window, chunk, status);
     return esp_launch_status();
 }

@@ -86,6 +86,14 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
     return scratch[32];
 }
 
+// Which keys a query sees, in every attention kernel of this library: key j from position pos iff first <= j <= pos
+// with first = 0 (every earlier key), pos - window + 1 (the last ``window``), or (chunk > 0) the start of the query's
+// own block of ``chunk`` positions counted from the sequence's start.
+__host__ __device__ __forceinline__ int first_visible_key(int pos, int window, int chunk) {
+    if (chunk > 0) return pos - pos % chunk;
+    return window > 0 ? (pos - window + 1 > 0 ? pos - window + 1 : 0) : 0;
+}
+
 // Launch-error helper: the C entry points return cudaGetLastError() as an int.
 static inline int esp_launch_status() { return (int)cudaGetLastError(); }
 

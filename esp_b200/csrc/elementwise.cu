@@ -629,3 +629,180 @@ ESP_API int esp_relu2(const float* z, const float* row_scale, void* act, int act
         esp_launch_pdl(ESP_PDL_SMALL, relu2_kernel<float>, dim3((int)blocks), dim3(256), 0, stream, z, row_scale, (float*)act, rows, width);
     return esp_launch_status();
 }
+
+// ---------------------------------------------------------------- hyper-connections
+// A layer over S copies of the residual stream, streams[s, row, :] (float).  One launch does, for every row it is
+// given, what lies between two sublayers:
+//   1. (y given) the write of the sublayer that has just run, all copies at once from the old ones:
+//          new_t = sum_s mix[s, t] old_s + out_w[t] y            (old_s = x0 for every s when x0 is given: the copies
+//                                                                  of a stack's first layer all equal what enters it)
+//   2. the read of the sublayer that comes next: u = sum_s read_w[s] new_s (read_w null: the plain sum, which is what
+//      leaves the stack), h = u / sqrt(mean(u^2) + eps) * gamma in the activation dtype, u itself to u_out.
+// ``rows`` selects the rows (the model's last norm wants a few); with write_streams 0 the copies are left as they are.
+// Every sum runs in ascending s, a row's sum of squares over a block of fixed size: a row's result depends on the row
+// alone.  A thread owns its channels in both passes, so it may overwrite the copies in the second.
+constexpr int HC_MAX_STREAMS = 8;
+
+template <typename T>
+__global__ void hc_step_kernel(float* __restrict__ streams, const float* __restrict__ x0, const float* __restrict__ y,
+                               const float* __restrict__ mix, const float* __restrict__ out_w,
+                               const float* __restrict__ read_w, const float* __restrict__ gamma,
+                               const int* __restrict__ rows, T* __restrict__ h, float* __restrict__ u_out, int S,
+                               long long stream_stride, int width, float eps, int write_streams) {
+    pdl_trigger();
+    __shared__ float s_mix[HC_MAX_STREAMS * HC_MAX_STREAMS], s_out[HC_MAX_STREAMS], s_read[HC_MAX_STREAMS];
+    __shared__ float scratch[33];
+    const int tid = threadIdx.x;
+    if (tid < S * S) s_mix[tid] = mix ? mix[tid] : (tid / S == tid % S ? 1.f : 0.f);
+    if (tid < S) {
+        s_out[tid] = out_w ? out_w[tid] : 0.f;
+        s_read[tid] = read_w ? read_w[tid] : 1.f;
+    }
+    __syncthreads();
+    pdl_wait();
+    const int i = blockIdx.x;
+    const size_t r = rows ? (size_t)rows[i] : (size_t)i;
+    const float* yrow = y ? y + r * width : nullptr;
+    const float* x0row = x0 ? x0 + r * width : nullptr;
+    float* srow = streams + r * width;
+    float ss = 0.f;
+    for (int pass = 0; pass < 2; pass++) {
+        if (pass == 1 && !write_streams && !h && !u_out) break;
+        float inv = 0.f;
+        if (pass == 1) inv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)width + eps);
+        for (int d = tid; d < width; d += blockDim.x) {
+            float old[HC_MAX_STREAMS], now[HC_MAX_STREAMS];
+#pragma unroll
+            for (int s = 0; s < HC_MAX_STREAMS; s++)
+                if (s < S) old[s] = x0row ? x0row[d] : srow[(size_t)s * stream_stride + d];
+            if (yrow) {
+                const float yv = yrow[d];
+#pragma unroll
+                for (int t = 0; t < HC_MAX_STREAMS; t++) {
+                    if (t >= S) break;
+                    float a = 0.f;
+#pragma unroll
+                    for (int s = 0; s < HC_MAX_STREAMS; s++)
+                        if (s < S) a = fmaf(s_mix[s * S + t], old[s], a);
+                    now[t] = fmaf(s_out[t], yv, a);
+                }
+            } else {
+#pragma unroll
+                for (int s = 0; s < HC_MAX_STREAMS; s++)
+                    if (s < S) now[s] = old[s];
+            }
+            float u = 0.f;
+#pragma unroll
+            for (int s = 0; s < HC_MAX_STREAMS; s++)
+                if (s < S) u = fmaf(s_read[s], now[s], u);
+            if (pass == 0) {
+                ss = fmaf(u, u, ss);
+            } else {
+                if (write_streams && (yrow || x0row)) {
+#pragma unroll
+                    for (int s = 0; s < HC_MAX_STREAMS; s++)
+                        if (s < S) srow[(size_t)s * stream_stride + d] = now[s];
+                }
+                if (u_out) u_out[r * width + d] = u;
+                if (h) h[(size_t)i * width + d] = from_f32<T>(u * inv * gamma[d]);
+            }
+        }
+    }
+}
+
+ESP_API int esp_hc_step(float* streams, const float* x0, const float* y, const float* mix, const float* out_w,
+                        const float* read_w, const float* gamma, const int* rows, void* h, int h_is_bf16, float* u_out,
+                        int n_streams, long long stream_stride, int n_rows, int width, float eps, int write_streams,
+                        cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    if (n_streams < 1 || n_streams > HC_MAX_STREAMS || width <= 0 || (h && !gamma)) return (int)cudaErrorInvalidValue;
+    const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
+    if (h_is_bf16)
+        esp_launch_pdl(ESP_PDL_SMALL, hc_step_kernel<bf16>, dim3(n_rows), dim3(threads), 0, stream, streams, x0, y, mix, out_w,
+                       read_w, gamma, rows, (bf16*)h, u_out, n_streams, stream_stride, width, eps, write_streams);
+    else
+        esp_launch_pdl(ESP_PDL_SMALL, hc_step_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, streams, x0, y, mix, out_w,
+                       read_w, gamma, rows, (float*)h, u_out, n_streams, stream_stride, width, eps, write_streams);
+    return esp_launch_status();
+}
+
+// ---------------------------------------------------------------- gated unit with clamped branches
+// act[m, i] = g sigmoid(alpha g) (u + shift) with g = min(gu[m, i], limit), u = clamp(gu[m, inter + i], -limit, limit);
+// gu is [rows, 2 * inter] in 32-bit.
+template <typename TO>
+__global__ void glu_clamped_kernel(const float* __restrict__ gu, TO* __restrict__ act, long long rows, int inter, float limit,
+                                   float alpha, float shift) {
+    pdl_trigger();
+    pdl_wait();
+    const long long total = rows * inter;
+    for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
+         idx += (long long)gridDim.x * blockDim.x) {
+        const long long m = idx / inter;
+        const int i = (int)(idx - m * inter);
+        const float g = fminf(gu[m * 2 * inter + i], limit);
+        const float u = fminf(fmaxf(gu[m * 2 * inter + inter + i], -limit), limit);
+        act[idx] = from_f32<TO>(g / (1.0f + expf(-alpha * g)) * (u + shift));
+    }
+}
+
+ESP_API int esp_glu_clamped(const float* gu, void* act, int act_is_bf16, long long rows, int inter, float limit, float alpha,
+                            float shift, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    const long long total = rows * inter;
+    const int blocks = (int)((total + 255) / 256 > 148 * 16 ? 148 * 16 : (total + 255) / 256);
+    if (act_is_bf16)
+        esp_launch_pdl(ESP_PDL_SMALL, glu_clamped_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, gu, (bf16*)act, rows, inter, limit, alpha, shift);
+    else
+        esp_launch_pdl(ESP_PDL_SMALL, glu_clamped_kernel<float>, dim3(blocks), dim3(256), 0, stream, gu, (float*)act, rows, inter, limit, alpha, shift);
+    return esp_launch_status();
+}
+
+// ---------------------------------------------------------------- small helpers of composite mixers
+// out = sum_i scale[i] * src[i] over up to four float arrays of ``count`` values, added in the order given.
+__global__ void weighted_sum_kernel(float* __restrict__ out, const float* __restrict__ a, const float* __restrict__ b,
+                                    const float* __restrict__ c, const float* __restrict__ d, float sa, float sb, float sc,
+                                    float sd, long long count) {
+    pdl_trigger();
+    pdl_wait();
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < count; i += (long long)gridDim.x * blockDim.x) {
+        float v = sa * a[i];
+        if (b) v = fmaf(sb, b[i], v);
+        if (c) v = fmaf(sc, c[i], v);
+        if (d) v = fmaf(sd, d[i], v);
+        out[i] = v;
+    }
+}
+
+ESP_API int esp_weighted_sum(float* out, const float* a, const float* b, const float* c, const float* d, float sa, float sb,
+                             float sc, float sd, long long count, cudaStream_t stream) {
+    if (count <= 0) return 0;
+    if (!a) return (int)cudaErrorInvalidValue;
+    long long blocks = (count + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    esp_launch_pdl(ESP_PDL_SMALL, weighted_sum_kernel, dim3((int)blocks), dim3(256), 0, stream, out, a, b, c, d, sa, sb, sc, sd, count);
+    return esp_launch_status();
+}
+
+// dst[r, :] = src[r, c0 : c0 + width] in the activation dtype (src float with row stride ld).
+template <typename TO>
+__global__ void cast_cols_kernel(const float* __restrict__ src, long long ld, TO* __restrict__ dst, long long rows, int width) {
+    pdl_trigger();
+    pdl_wait();
+    const long long total = rows * width;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const long long r = i / width;
+        dst[i] = from_f32<TO>(src[r * ld + (i - r * width)]);
+    }
+}
+
+ESP_API int esp_cast_cols(const float* src, long long ld, void* dst, int dst_is_bf16, long long rows, int width,
+                          cudaStream_t stream) {
+    if (rows <= 0 || width <= 0) return 0;
+    long long blocks = (rows * width + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (dst_is_bf16)
+        esp_launch_pdl(ESP_PDL_SMALL, cast_cols_kernel<bf16>, dim3((int)blocks), dim3(256), 0, stream, src, ld, (bf16*)dst, rows, width);
+    else
+        esp_launch_pdl(ESP_PDL_SMALL, cast_cols_kernel<float>, dim3((int)blocks), dim3(256), 0, stream, src, ld, (float*)dst, rows, width);
+    return esp_launch_status();
+}

@@ -32,7 +32,7 @@ _SIGNATURES = {
     "esp_gate_prepare": [c_int, P, c_longlong, P, c_longlong, P, P, P, P, P, c_longlong, c_int, P],
     "esp_gated_scan": [c_int, c_int, P, c_longlong, P, c_longlong, P, c_longlong, P, c_longlong, P, P, P, P, c_longlong, P, P, P,
                        c_int, c_int, c_int, c_int, P],
-    "esp_head_rmsnorm_gate": [P, P, c_int, P, c_longlong, P, c_int, c_int, c_int, c_int, c_float, P],
+    "esp_head_rmsnorm_gate": [P, P, c_int, P, c_longlong, P, c_int, c_int, c_int, c_int, c_float, c_int, P],
     "esp_latent_kv_store": [P, P, P, c_float, c_int, P, P, P, c_int, c_int, c_int, P, c_int, c_int, c_int, c_int, c_float, P,
                             P],
     "esp_latent_q_rotate": [P, P, c_float, c_int, P, P, c_int, c_int, c_int, c_int, c_int, c_int, P],
@@ -46,8 +46,8 @@ _SIGNATURES = {
     "esp_gemm_simt": [P, c_int, P, P, c_int, P, P, P, c_int, P, c_int, c_int, c_int, c_int, c_longlong, c_longlong, P],
     "esp_rope_kvwrite": [P, P, P, P, P, P, c_int, c_int, P, P, P, c_int, P, c_int, c_int, c_int, c_int, c_int, c_int,
                          c_int, c_int, P, P],
-    "esp_attn_simt": [P, P, P, P, c_int, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int,
-                      P, P],
+    "esp_attn_simt": [P, P, P, P, c_int, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, P,
+                      c_int, c_int, P, P],
     "esp_embed_sum": [P, P, c_int, P, P, P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_longlong, c_longlong, c_float, P, P],
     "esp_norm_add_rmsnorm": [P, P, P, c_float, P, P, P, c_int, P, c_int, c_int, c_float, c_int, P],
     "esp_relu2": [P, P, P, c_int, c_longlong, c_int, P],
@@ -58,6 +58,17 @@ _SIGNATURES = {
     "esp_matrix_memory_finish": [P, P, P, P, c_longlong, P, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_float, P],
     "esp_conv_branches": [P, P, P, P, P, P, c_longlong, P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, P],
     "esp_diag_scan": [P, P, P, P, c_float, P, P, P, c_longlong, P, P, P, c_int, c_int, c_int, c_int, c_int, P],
+    "esp_hc_step": [P, P, P, P, P, P, P, P, P, c_int, P, c_int, c_longlong, c_int, c_int, c_float, c_int, P],
+    "esp_glu_clamped": [P, P, c_int, c_longlong, c_int, c_float, c_float, c_float, P],
+    "esp_weighted_sum": [P, P, P, P, P, c_float, c_float, c_float, c_float, c_longlong, P],
+    "esp_cast_cols": [P, c_longlong, P, c_int, c_longlong, c_int, P],
+    "esp_widenorm_rope_kvwrite": [P, P, P, c_float, P, c_int, c_float, P, P, P, P, P, c_int, P, c_int, c_int, c_int, c_int,
+                                  c_int, c_int, c_int, c_int, c_int, P, P],
+    "esp_delta_scan": [P, c_longlong, P, c_longlong, P, c_longlong, P, c_longlong, P, P, c_longlong, P, P, P, c_int, c_int,
+                       c_int, c_int, c_int, P],
+    "esp_delta_prepare": [P, c_longlong, c_int, c_int, c_float, c_float, P, c_longlong, P, P, P, P, c_longlong, P, c_int, c_int, P],
+    "esp_channel_decay_prepare": [P, P, c_float, P, c_longlong, c_float, P, c_longlong, c_int, P],
+    "esp_causal_conv": [P, c_longlong, P, P, c_longlong, P, P, P, P, c_int, c_int, c_int, c_int, c_int, P],
     "esp_router_topk": [P, c_int, P, P, c_int, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, P, P],
     "esp_moe_permute": [P, P, c_int, c_int, c_int, P, P, P, P, P, P, P, P, c_int, c_int, P, P, P],
     "esp_gather_rows": [P, P, P, c_int, c_int, P],
@@ -331,19 +342,31 @@ def rope_kvwrite(qkv, bias, tok_seq, tok_pos, cos, sin, rot, q_out, k_cache, v_c
         nh, nkv, hd, 1 if write_kv else 0, _ptr(status, torch.int32), _stream()), "rope_kvwrite")
 
 
+def _sink_args(sink, nh):
+    """(flag, pointer) of a sink: True is one more term exp(0) in the softmax's denominator, a float32 tensor [heads]
+    the term exp(sink[head])."""
+    if isinstance(sink, torch.Tensor):
+        if sink.dtype != torch.float32 or sink.numel() != nh:
+            raise Backend("attention: the sinks must be one float32 number per query head")
+        return 1, _ptr(sink, torch.float32, "sink")
+    return (1 if sink else 0), None
+
+
 def attn_simt(q, k_cache, v_cache, out, tok_seq, tok_pos, block_table, page, nh, nkv, hd, window, status, vd=None,
-              scale=0.0, sink=False):
+              scale=0.0, sink=False, chunk=None):
     """Attention of every token over its sequence's cached keys (32-bit arithmetic).  ``vd``: size of a value head
     (default: the key size); ``scale`` > 0 multiplies the scores instead of the division by sqrt(hd); ``sink``: the
-    softmax's denominator holds one more term exp(0)."""
+    softmax's denominator holds one more term exp(0), or exp(sink[head]) when a tensor is given; ``chunk``: a query
+    sees the keys of its own block of that many positions only."""
+    sink_flag, sink_ptr = _sink_args(sink, nh)
     vd = hd if vd is None else vd
     if hd > 256 or vd > 256:
         raise Backend(f"attention: head sizes {hd} / {vd} are beyond the 256 this kernel takes")
     _check(_fn("core", "esp_attn_simt")(
         _ptr(q, FLOATS, "q"), _ptr(k_cache, FLOATS), _ptr(v_cache, FLOATS), _ptr(out, FLOATS), _is_bf16(q),
         _ptr(tok_seq, torch.int32), _ptr(tok_pos, torch.int32), _ptr(block_table, torch.int32), block_table.shape[1],
-        k_cache.shape[0], page, q.shape[0], nh, nkv, hd, vd, float(scale), 1 if sink else 0, int(window or 0),
-        _ptr(status, torch.int32), _stream()), "attn_simt")
+        k_cache.shape[0], page, q.shape[0], nh, nkv, hd, vd, float(scale), sink_flag, sink_ptr, int(window or 0),
+        int(chunk or 0), _ptr(status, torch.int32), _stream()), "attn_simt")
 
 
 def router_topk(h, w_router, w_gate, topk_ids, topk_w, gate, top_k, norm_topk, status, probs_out=None, logits=None,
@@ -763,13 +786,14 @@ def gated_scan(mode, q, k, g, v, gate_bias, lower, bonus, state, seq_start, seq_
         key_dim, value_dim, _stream()), "gated_scan")
 
 
-def head_rmsnorm_gate(o, weight, weight_head_stride, gate, y, heads, value_dim, eps):
-    """y[n, h] = o[n, h] / rms(o[n, h]) * weight[h * weight_head_stride + :] (* silu(gate[n, h])); o float32
-    [rows, heads * value_dim], gate float32 or None, y float32 or bfloat16."""
+def head_rmsnorm_gate(o, weight, weight_head_stride, gate, y, heads, value_dim, eps, gate_sigmoid=False):
+    """y[n, h] = o[n, h] / rms(o[n, h]) * weight[h * weight_head_stride + :] (* silu(gate[n, h]), or its sigmoid with
+    ``gate_sigmoid``); o float32 [rows, heads * value_dim], gate float32 or None, y float32 or bfloat16."""
     pg, ldg = _rows_ld(gate, "gate")
     _check(_fn("mixers", "esp_head_rmsnorm_gate")(
         _ptr(o, torch.float32, "o"), _ptr(weight, torch.float32, "weight"), int(weight_head_stride), pg, ldg,
-        _ptr(y, FLOATS, "y"), _is_bf16(y), o.shape[0], heads, value_dim, float(eps), _stream()), "head_rmsnorm_gate")
+        _ptr(y, FLOATS, "y"), _is_bf16(y), o.shape[0], heads, value_dim, float(eps), 1 if gate_sigmoid else 0, _stream()),
+        "head_rmsnorm_gate")
 
 
 def latent_kv_store(d, norm_w, inv_freq, magnitude, rot_dims, tok_seq, tok_pos, block_table, pool, page, rank, rot, eps, status):
@@ -979,3 +1003,128 @@ def diag_scan(gates, bias_r, bias_i, lam, decay_scale, u, gate, state, seq_start
         _ptr(lam, torch.float32), float(decay_scale), _ptr(u, torch.float32), _ptr(gate, torch.float32), state.data_ptr(),
         state.stride(0), _ptr(seq_start, torch.int32), _ptr(seq_slot, torch.int32), _ptr(out, FLOATS), _is_bf16(out),
         gates.shape[0], n_seqs, channels, blocks, _stream()), "diag_scan")
+
+
+# ---------------------------------------------------------------------------
+HC_MAX_STREAMS = 8
+
+
+def hc_step(streams, h, gamma, eps, x0=None, y=None, mix=None, out_w=None, read_w=None, rows=None, u_out=None,
+            write_streams=True):
+    """What lies between two sublayers of a layer over several copies of the residual stream (``streams`` float32
+    [S, rows, width]): with ``y`` the write of the sublayer that ran, new_t = sum_s mix[s, t] old_s + out_w[t] y (the old
+    copies all equal ``x0`` when that is given); then the read of the next one, u = sum_s read_w[s] new_s (the plain sum
+    without ``read_w``), ``h`` = rmsnorm(u) * gamma in its dtype (None: no norm), ``u_out`` = u.  ``rows`` (int32)
+    selects rows; h has one row per selected row."""
+    n_streams, n_total, width = streams.shape
+    if n_streams > HC_MAX_STREAMS:
+        raise Backend(f"hc_step: {n_streams} streams are beyond the {HC_MAX_STREAMS} this kernel takes")
+    n_rows = rows.shape[0] if rows is not None else n_total
+    if h is not None and (h.shape[0] != n_rows or h.shape[1] != width):
+        raise Backend("hc_step: h does not fit the rows")
+    _check(_fn("core", "esp_hc_step")(
+        _ptr(streams, torch.float32, "streams"), _ptr(x0, torch.float32, "x0"), _ptr(y, torch.float32, "y"),
+        _ptr(mix, torch.float32, "mix"), _ptr(out_w, torch.float32, "out_w"), _ptr(read_w, torch.float32, "read_w"),
+        _ptr(gamma, torch.float32, "gamma"), _ptr(rows, torch.int32, "rows"), _ptr(h, FLOATS, "h"),
+        _is_bf16(h) if h is not None else 0, _ptr(u_out, torch.float32, "u_out"), n_streams, n_total * width, n_rows, width,
+        float(eps), 1 if write_streams else 0, _stream()), "hc_step")
+
+
+def glu_clamped(gu, act, limit, alpha, shift):
+    """act = g sigmoid(alpha g) (u + shift), g = min(gu[:, :I], limit), u = clamp(gu[:, I:], -limit, limit); gu float32
+    [rows, 2I], act float32 or bfloat16 [rows, I]."""
+    rows, inter = act.shape
+    if tuple(gu.shape) != (rows, 2 * inter):
+        raise Backend("glu_clamped: shapes disagree")
+    _check(_fn("core", "esp_glu_clamped")(_ptr(gu, torch.float32, "gu"), _ptr(act, FLOATS, "act"), _is_bf16(act), rows, inter,
+                                           float(limit), float(alpha), float(shift), _stream()), "glu_clamped")
+
+
+def weighted_sum(out, parts, scales):
+    """out = sum_i scales[i] * parts[i] over up to four float32 tensors of out's size, added in the order given."""
+    if not 1 <= len(parts) <= 4 or len(scales) != len(parts):
+        raise Backend("weighted_sum: one to four parts with a scale each")
+    ptrs = [_ptr(p, torch.float32, "part") for p in parts] + [None] * (4 - len(parts))
+    sc = [float(v) for v in scales] + [0.0] * (4 - len(parts))
+    if any(p.numel() != out.numel() for p in parts):
+        raise Backend("weighted_sum: sizes disagree")
+    _check(_fn("core", "esp_weighted_sum")(_ptr(out, torch.float32, "out"), *ptrs, *sc, out.numel(), _stream()), "weighted_sum")
+
+
+def cast_cols(src, dst):
+    """dst = src in dst's dtype; src float32 rows that may be parts of wider rows."""
+    p, ld = _rows_ld(src, "src")
+    if tuple(dst.shape) != tuple(src.shape):
+        raise Backend("cast_cols: shapes disagree")
+    _check(_fn("core", "esp_cast_cols")(p, ld, _ptr(dst, FLOATS, "dst"), _is_bf16(dst), src.shape[0], src.shape[1], _stream()),
+           "cast_cols")
+
+
+def widenorm_rope_kvwrite(qkv, q_w, k_w, eps, inv_freq, rot, v_scale, tok_seq, tok_pos, q_out, k_cache, v_cache, block_table,
+                          page, nh, nkv, hd, vd, write_kv, status):
+    """Queries and keys normed over their whole projection (weights q_w [nh * hd], k_w [nkv * hd]), the first ``rot``
+    channels of every head rotated by position * inv_freq, values times v_scale; queries to q_out, keys and values to the
+    paged cache.  qkv float32 [rows, nh * hd + nkv * hd + nkv * vd]."""
+    if qkv.shape[1] != nh * hd + nkv * hd + nkv * vd:
+        raise Backend("widenorm_rope_kvwrite: the projection's width does not fit the head sizes")
+    if rot and (inv_freq is None or inv_freq.shape[0] < rot // 2):
+        raise Backend("widenorm_rope_kvwrite: too few frequencies")
+    _check(_fn("core", "esp_widenorm_rope_kvwrite")(
+        _ptr(qkv, torch.float32, "qkv"), _ptr(q_w, torch.float32, "q_w"), _ptr(k_w, torch.float32, "k_w"), float(eps),
+        _ptr(inv_freq, torch.float32, "inv_freq"), int(rot), float(v_scale), _ptr(tok_seq, torch.int32),
+        _ptr(tok_pos, torch.int32), _ptr(q_out, FLOATS, "q_out"), _ptr(k_cache, q_out.dtype, "k_cache"),
+        _ptr(v_cache, q_out.dtype, "v_cache"), _is_bf16(q_out), _ptr(block_table, torch.int32), block_table.shape[1],
+        k_cache.shape[0], page, qkv.shape[0], nh, nkv, hd, vd, 1 if write_kv else 0, _ptr(status, torch.int32), _stream()),
+        "widenorm_rope_kvwrite")
+
+
+def delta_scan(q, k, d, v, beta, state, seq_start, seq_slot, out, n_seqs, heads, kv_heads, key_dim, value_dim):
+    """The delta rule with a decay per key channel over the runs of rows that the sequences bring, from and to ``state``
+    (float32 [slots, >= heads * value_dim * key_dim], a head's block laid out [value_dim, key_dim]): S <- diag(d) S;
+    u = beta (v - S^T k); S <- S + k u^T; o = S^T q.  q, k: float32 [rows, kv_heads * key_dim]; d: [rows, heads * key_dim];
+    v, out: [rows, heads * value_dim]; beta: [rows, heads].  All 32-bit."""
+    if key_dim > SCAN_MAX_KEY_DIM:
+        raise Backend(f"delta_scan: {key_dim} key channels per head are beyond the {SCAN_MAX_KEY_DIM} this kernel takes")
+    if state.dtype != torch.float32 or state.stride(1) != 1 or state.shape[1] < heads * key_dim * value_dim:
+        raise Backend("delta_scan: the state rows are too short or not float32")
+    (pq, ldq), (pk, ldk), (pd, ldd), (pv, ldv) = (_rows_ld(t, n) for t, n in ((q, "q"), (k, "k"), (d, "d"), (v, "v")))
+    _check(_fn("mixers", "esp_delta_scan")(
+        pq, ldq, pk, ldk, pd, ldd, pv, ldv, _ptr(beta, torch.float32, "beta"), state.data_ptr(), state.stride(0),
+        _ptr(seq_start, torch.int32), _ptr(seq_slot, torch.int32), _ptr(out, torch.float32, "out"), int(n_seqs), heads,
+        kv_heads, key_dim, value_dim, _stream()), "delta_scan")
+
+
+def delta_prepare(qk, kv_heads, key_dim, unit_eps, q_scale, raw, decay, dt_bias, a_log, b_raw, beta, heads):
+    """The kv_heads query heads at column 0 of ``qk`` and the key heads behind them become unit vectors in place
+    (queries times q_scale); decay = exp(-exp(a_log[h]) softplus(raw + dt_bias)) (float32 [rows, heads * key_dim], raw
+    rows that may be parts of wider rows); beta = sigmoid(b_raw)."""
+    (pqk, ldqk), (pb, ldb), (praw, ldraw) = _rows_ld(qk, "qk"), _rows_ld(b_raw, "b_raw"), _rows_ld(raw, "raw")
+    _check(_fn("mixers", "esp_delta_prepare")(
+        pqk, ldqk, kv_heads, key_dim, float(unit_eps), float(q_scale), praw, ldraw, _ptr(decay, torch.float32, "decay"),
+        _ptr(dt_bias, torch.float32, "dt_bias"), _ptr(a_log, torch.float32, "a_log"), pb, ldb,
+        _ptr(beta, torch.float32, "beta"), heads, qk.shape[0], _stream()), "delta_prepare")
+
+
+def channel_decay_prepare(z, bias, tau, q, q_scale, q_out):
+    """In place z = sigmoid(z + bias)^(1 / tau); q_out = q * q_scale (q float32 rows that may be parts of wider rows)."""
+    pq, ldq = _rows_ld(q, "q")
+    _check(_fn("mixers", "esp_channel_decay_prepare")(
+        _ptr(z, torch.float32, "z"), _ptr(bias, torch.float32, "bias"), float(tau), pq, ldq, float(q_scale),
+        _ptr(q_out, torch.float32, "q_out"), z.shape[0], z.shape[1], _stream()), "channel_decay_prepare")
+
+
+def causal_conv(x, w, conv_state, tok_seq, seq_start, seq_slot, y, n_seqs, taps, silu=True):
+    """y = act(causal convolution of x over ``taps`` positions per channel) within every sequence (w float32 [C, taps],
+    last column the token's own); conv_state float32 [slots, (taps - 1) * C] (a view with its slot stride) holds a
+    sequence's last taps - 1 inputs and is brought up to date.  x float32 rows that may be parts of wider rows."""
+    if taps > CONV_MAX_TAPS:
+        raise Backend(f"causal_conv: {taps} taps are beyond the {CONV_MAX_TAPS} this kernel takes")
+    px, ldx = _rows_ld(x, "x")
+    channels = x.shape[1]
+    if tuple(y.shape) != tuple(x.shape) or tuple(w.shape) != (channels, taps):
+        raise Backend("causal_conv: shapes disagree")
+    _check(_fn("mixers", "esp_causal_conv")(
+        px, ldx, _ptr(w, torch.float32, "w"), conv_state.data_ptr() if conv_state is not None else None,
+        conv_state.stride(0) if conv_state is not None else 0, _ptr(tok_seq, torch.int32), _ptr(seq_start, torch.int32),
+        _ptr(seq_slot, torch.int32), _ptr(y, torch.float32, "y"), x.shape[0], int(n_seqs), channels, taps, 1 if silu else 0,
+        _stream()), "causal_conv")

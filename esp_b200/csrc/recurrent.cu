@@ -324,12 +324,13 @@ __global__ void gate_prepare_kernel(const float* __restrict__ q, long long ldq, 
 }
 
 // ---------------------------------------------------------------------------------------------- norm of the heads
-// y[n, h, :] = o[n, h, :] / sqrt(mean(o[n, h, :]^2) + eps) * w[h * w_head_stride + :] (* silu(gate[n, h, :]))
+// y[n, h, :] = o[n, h, :] / sqrt(mean(o[n, h, :]^2) + eps) * w[h * w_head_stride + :] (* silu(gate[n, h, :]), or, with
+// gate_sigmoid, * sigmoid(gate[n, h, :]))
 // One warp per (row, head).
 template <typename T>
 __global__ void head_rmsnorm_gate_kernel(const float* __restrict__ o, const float* __restrict__ w, int w_head_stride,
                                          const float* __restrict__ gate, long long ldgate, T* __restrict__ y, int n_rows,
-                                         int H, int V, float eps) {
+                                         int H, int V, float eps, int gate_sigmoid) {
     pdl_trigger();
     pdl_wait();
     const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
@@ -355,7 +356,7 @@ __global__ void head_rmsnorm_gate_kernel(const float* __restrict__ o, const floa
             const int i = lane + 32 * j;
             if (i >= V) break;
             float r = val[j] * inv * w[h * w_head_stride + i];
-            if (gate) r *= gz[j] / (1.0f + expf(-gz[j]));
+            if (gate) r *= (gate_sigmoid ? 1.0f : gz[j]) / (1.0f + expf(-gz[j]));
             y[((size_t)n * H + h) * V + i] = from_f32<T>(r);
         }
         return;
@@ -367,7 +368,7 @@ __global__ void head_rmsnorm_gate_kernel(const float* __restrict__ o, const floa
         float r = src[i] * inv * w[h * w_head_stride + i];
         if (gate) {
             const float z = gate[(size_t)n * ldgate + h * V + i];
-            r *= z / (1.0f + expf(-z));
+            r *= (gate_sigmoid ? 1.0f : z) / (1.0f + expf(-z));
         }
         y[((size_t)n * H + h) * V + i] = from_f32<T>(r);
     }
@@ -730,16 +731,17 @@ ESP_API int esp_gated_scan(int mode, int ready, const float* q, long long ldq, c
 }
 
 ESP_API int esp_head_rmsnorm_gate(const float* o, const float* w, int w_head_stride, const float* gate, long long ldgate,
-                                  void* y, int y_is_bf16, int n_rows, int H, int V, float eps, cudaStream_t stream) {
+                                  void* y, int y_is_bf16, int n_rows, int H, int V, float eps, int gate_sigmoid,
+                                  cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     const long long warps = (long long)n_rows * H;
     const int blocks = (int)((warps + 7) / 8);
     if (y_is_bf16)
         esp_launch_pdl(ESP_PDL_SMALL, head_rmsnorm_gate_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, o, w, w_head_stride,
-                       gate, ldgate, (bf16*)y, n_rows, H, V, eps);
+                       gate, ldgate, (bf16*)y, n_rows, H, V, eps, gate_sigmoid);
     else
         esp_launch_pdl(ESP_PDL_SMALL, head_rmsnorm_gate_kernel<float>, dim3(blocks), dim3(256), 0, stream, o, w, w_head_stride,
-                       gate, ldgate, (float*)y, n_rows, H, V, eps);
+                       gate, ldgate, (float*)y, n_rows, H, V, eps, gate_sigmoid);
     return esp_launch_status();
 }
 

@@ -259,3 +259,94 @@ ESP_API int esp_qknorm_kvwrite(const float* qkv, const float* bias, const float*
                        block_table, table_stride, n_pages, page, nh, nkv, hd, vd, write_kv, status);
     return esp_launch_status();
 }
+
+// ---------------------------------------------------------------- norms over the whole projection, partial rotation
+// qkv: [n_tokens, nh*hd + nkv*hd + nkv*vd] float.  The queries of a token, all heads together, are divided by their
+// root mean square over the nh*hd channels (eps inside the root) and multiplied by a weight per channel (q_w, nh*hd
+// numbers); the keys likewise over nkv*hd channels with k_w (null: that side is left as projected).  Then the first
+// ``rot`` channels of every head are rotated, channel i with channel i + rot/2, by the angle position * inv_freq[i]
+// (a 32-bit product; sine and cosine in 32-bit); the other channels pass unchanged.  Values are multiplied by v_scale.
+// Queries go to q_out [n_tokens, nh, hd], keys [pages, nkv, PAGE, hd] and values [pages, nkv, PAGE, vd] to the
+// token's place in the paged cache.  One block per token.
+template <typename T>
+__global__ void widenorm_rope_kvwrite_kernel(const float* __restrict__ qkv, const float* __restrict__ q_w,
+                                             const float* __restrict__ k_w, float eps, const float* __restrict__ inv_freq,
+                                             int rot, float v_scale, const int* __restrict__ tok_seq,
+                                             const int* __restrict__ tok_pos, T* __restrict__ q_out, T* __restrict__ k_cache,
+                                             T* __restrict__ v_cache, const int* __restrict__ block_table, int table_stride,
+                                             int n_pages, int page, int nh, int nkv, int hd, int vd, int write_kv,
+                                             int* __restrict__ status) {
+    pdl_trigger();
+    pdl_wait();
+    __shared__ float scratch[33];
+    const int n = blockIdx.x, tid = threadIdx.x;
+    const int pos = tok_pos[n], seq = tok_seq[n];
+    const int qw = nh * hd, kw = nkv * hd, vw = nkv * vd;
+    const float* src = qkv + (size_t)n * (qw + kw + vw);
+    int page_id = -1;
+    if (write_kv) {
+        page_id = block_table[(size_t)seq * table_stride + pos / page];
+        if (page_id < 0 || page_id >= n_pages) {
+            if (tid == 0) atomicOr(status, ESP_STATUS_BAD_INDEX);
+            page_id = -1;
+        }
+    }
+    const int in_page = pos % page;
+    float ssq = 0.f, ssk = 0.f;
+    for (int e = tid; e < qw; e += blockDim.x) ssq = fmaf(src[e], src[e], ssq);
+    for (int e = tid; e < kw; e += blockDim.x) ssk = fmaf(src[qw + e], src[qw + e], ssk);
+    const float inv_q = q_w ? 1.0f / sqrtf(block_sum(ssq, scratch) / (float)qw + eps) : 1.0f;
+    const float inv_k = k_w ? 1.0f / sqrtf(block_sum(ssk, scratch) / (float)kw + eps) : 1.0f;
+    const int half = rot / 2;
+    const float p = (float)pos;
+    for (int e = tid; e < qw + kw; e += blockDim.x) {
+        const bool is_q = e < qw;
+        const int local = is_q ? e : e - qw;
+        const int head = local / hd, c = local - head * hd;
+        if (c >= half && c < rot) continue;               // the second half of a pair is written with the first
+        const float* w = is_q ? q_w : k_w;
+        const float inv = is_q ? inv_q : inv_k;
+        T* dst;
+        if (is_q) dst = q_out + ((size_t)n * nh + head) * hd;
+        else if (page_id >= 0) dst = k_cache + (((size_t)page_id * nkv + head) * page + in_page) * hd;
+        else continue;
+        float a = src[e];
+        if (w) a = a * inv * w[local];
+        if (c < half) {
+            float b = src[e + half];
+            if (w) b = b * inv * w[local + half];
+            float sn, cs;
+            sincosf(p * inv_freq[c], &sn, &cs);
+            dst[c] = from_f32<T>(a * cs - b * sn);
+            dst[c + half] = from_f32<T>(b * cs + a * sn);
+        } else {
+            dst[c] = from_f32<T>(a);
+        }
+    }
+    if (page_id >= 0) {
+        for (int e = tid; e < vw; e += blockDim.x) {
+            const int head = e / vd, c = e - head * vd;
+            v_cache[(((size_t)page_id * nkv + head) * page + in_page) * vd + c] = from_f32<T>(src[qw + kw + e] * v_scale);
+        }
+    }
+}
+
+ESP_API int esp_widenorm_rope_kvwrite(const float* qkv, const float* q_w, const float* k_w, float eps, const float* inv_freq,
+                                      int rot, float v_scale, const int* tok_seq, const int* tok_pos, void* q_out,
+                                      void* k_cache, void* v_cache, int is_bf16, const int* block_table, int table_stride,
+                                      int n_pages, int page, int n_tokens, int nh, int nkv, int hd, int vd, int write_kv,
+                                      int* status, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (hd <= 0 || vd <= 0 || nkv <= 0 || nh <= 0 || page <= 0 || rot < 0 || rot > hd || rot % 2 != 0 || (rot > 0 && !inv_freq))
+        return (int)cudaErrorInvalidValue;
+    const int threads = (nh + nkv) * hd >= 2048 ? 256 : 128;
+    if (is_bf16)
+        esp_launch_pdl(ESP_PDL_SMALL, widenorm_rope_kvwrite_kernel<bf16>, dim3(n_tokens), dim3(threads), 0, stream, qkv, q_w, k_w,
+                       eps, inv_freq, rot, v_scale, tok_seq, tok_pos, (bf16*)q_out, (bf16*)k_cache, (bf16*)v_cache, block_table,
+                       table_stride, n_pages, page, nh, nkv, hd, vd, write_kv, status);
+    else
+        esp_launch_pdl(ESP_PDL_SMALL, widenorm_rope_kvwrite_kernel<float>, dim3(n_tokens), dim3(threads), 0, stream, qkv, q_w, k_w,
+                       eps, inv_freq, rot, v_scale, tok_seq, tok_pos, (float*)q_out, (float*)k_cache, (float*)v_cache,
+                       block_table, table_stride, n_pages, page, nh, nkv, hd, vd, write_kv, status);
+    return esp_launch_status();
+}

@@ -369,7 +369,8 @@ class Engine:
             for p, t in zip(pasts, news):
                 # the keys the sequence's last new token sees: every kernel streams a sequence's visible keys once
                 last = p + t
-                seen += last if layout.window is None else min(last, layout.window + t - 1)
+                span = layout.window if layout.window is not None else layout.chunk
+                seen += last if span is None else min(last, span + t - 1)
             c["kv_bytes_read"] += seen * per_key
 
     def profile_step(self, entries: list):

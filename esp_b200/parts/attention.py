@@ -322,5 +322,102 @@ class NormedAttention(Part):
         return y
 
 
+class WideNormAttention(Part):
+    """Causal softmax attention over the paged cache whose query and key norms run over the whole projection (see
+    ``WideNormAttentionSpec``): packed q/k/v projection; one kernel norms queries and keys over all their heads at
+    once, rotates the first channels of every head and stores keys (normed and rotated) and values in the cache;
+    the attention kernels take the scores' scale as given, a mask of blocks counted from the sequence's start
+    (``chunk``) or a window, and a learned sink per head.  Query head i reads key/value head
+    i // (num_heads / num_kv_heads)."""
+
+    graph_safe = True
+
+    def __init__(self, spec, rt):
+        self.spec, self.rt = spec, rt
+        s = spec
+        if s.key_dim > 256 or s.value_dim > 256:
+            raise Unsupported("dim", f"{s.key_dim} / {s.value_dim}; the attention kernels take head sizes up to 256")
+        if s.num_heads % s.num_kv_heads != 0:
+            raise Unsupported("kv_heads", f"{s.num_kv_heads} does not divide {s.num_heads} heads")
+        if s.window is not None and s.chunk is not None:
+            raise Unsupported("mask", "a window and a mask of blocks on the same layer")
+        self.q_width = s.num_heads * s.key_dim
+        self.k_width = s.num_kv_heads * s.key_dim
+        self.v_width = s.num_kv_heads * s.value_dim
+        self.o_width = s.num_heads * s.value_dim
+        self.qkv_width = self.q_width + self.k_width + self.v_width
+        self.position = None
+        if s.position is not None:
+            if getattr(s.position, "factor", None) is not None:
+                raise Unsupported("rot", "interpolated frequencies on an attention layer with norms over the whole projection")
+            key = ("position", s.position)            # layers with the same encoding share one part (and its frequencies)
+            if key not in rt.shared_parts:
+                rt.shared_parts[key] = build("position", s.position, rt)
+            self.position = rt.shared_parts[key]
+        self.w_qkv = self.w_o = self.q_norm = self.k_norm = self.sink = None
+
+    def children(self):
+        return [self.position] if self.position is not None else []
+
+    def _n(self, which):
+        return self.spec.prefix + getattr(self.spec.names, which)
+
+    def param_specs(self):
+        s = self.spec
+        specs = [ParamSpec(self._n("q"), (self.q_width, s.hidden), "matrix"),
+                 ParamSpec(self._n("k"), (self.k_width, s.hidden), "matrix"),
+                 ParamSpec(self._n("v"), (self.v_width, s.hidden), "matrix"),
+                 ParamSpec(self._n("o"), (s.hidden, self.o_width), "matrix"),
+                 ParamSpec(self._n("q_norm"), (self.q_width,), "norm_scale"),
+                 ParamSpec(self._n("k_norm"), (self.k_width,), "norm_scale")]
+        if s.learned_sink:
+            specs.append(ParamSpec(self._n("sink"), (s.num_heads,), "attention_sink", init=(0.0, 1.0)))
+        return specs
+
+    def allocate(self, stored, rt):
+        s, dev = self.spec, rt.device
+        names = [self._n("q"), self._n("k"), self._n("v")]
+        self.w_qkv = torch.empty((self.qkv_width, s.hidden), dtype=rt.matrix_dtype([stored[n] for n in names]), device=dev)
+        self.w_o = torch.empty((s.hidden, self.o_width), dtype=rt.matrix_dtype([stored[self._n("o")]]), device=dev)
+        self.q_norm = torch.empty(self.q_width, dtype=torch.float32, device=dev)
+        self.k_norm = torch.empty(self.k_width, dtype=torch.float32, device=dev)
+        a, b = self.q_width, self.q_width + self.k_width
+        views = {names[0]: self.w_qkv[:a], names[1]: self.w_qkv[a:b], names[2]: self.w_qkv[b:], self._n("o"): self.w_o,
+                 self._n("q_norm"): self.q_norm, self._n("k_norm"): self.k_norm}
+        if s.learned_sink:
+            self.sink = torch.empty(s.num_heads, dtype=torch.float32, device=dev)
+            views[self._n("sink")] = self.sink
+        return views
+
+    def kv_layout(self):
+        s = self.spec
+        return KvLayout(s.num_kv_heads, s.key_dim, s.window, value_dim=s.value_dim if s.value_dim != s.key_dim else None,
+                        chunk=s.chunk)
+
+    def state_spec(self):
+        return None
+
+    def forward(self, h, ctx, layer):
+        s, rt = self.spec, self.rt
+        n = h.shape[0]
+        table = ctx.block_tables[layer.group]
+        qkv = rt.ws.get("attn_qkv", (n, self.qkv_width), torch.float32)
+        linear(rt, h, self.w_qkv, qkv)
+        q = rt.ws.get("attn_q", (n, self.q_width), rt.dtype)
+        pos = self.position
+        ops.widenorm_rope_kvwrite(qkv, self.q_norm, self.k_norm, s.eps, pos.inv_freq if pos is not None else None,
+                                  pos.spec.rotary_dim if pos is not None else 0, 1.0, ctx.tok_seq, ctx.tok_pos, q, layer.k,
+                                  layer.v, table, layer.page, s.num_heads, s.num_kv_heads, s.key_dim, s.value_dim, layer.writes,
+                                  rt.status)
+        o = rt.ws.get("attn_o", (n, self.o_width), rt.dtype)
+        ops.attn_simt(q, layer.k, layer.v, o, ctx.tok_seq, ctx.tok_pos, table, layer.page, s.num_heads, s.num_kv_heads,
+                      s.key_dim, s.window, rt.status, vd=s.value_dim, scale=s.scale,
+                      sink=self.sink if s.learned_sink else False, chunk=s.chunk)
+        y = rt.ws.get("mixer_out", (n, s.hidden), torch.float32)
+        linear(rt, o, self.w_o, y)
+        return y
+
+
 register("mixer", "attention", Attention)
 register("mixer", "attention_qknorm", NormedAttention)
+register("mixer", "attention_widenorm", WideNormAttention)

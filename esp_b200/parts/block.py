@@ -4,6 +4,7 @@ from __future__ import annotations
 import torch
 
 from ..csrc import ops
+from ..errors import Backend, Unsupported
 from .base import ParamSpec, Part, build, plain_delta, register
 from .norm import DeferredPostNorm
 
@@ -151,6 +152,111 @@ class SandwichBlock(Part):
         return pending
 
 
+class DeferredStreamWrite:
+    """The write of a sublayer into the copies of the residual stream, on its way to whoever reads them next: the
+    next layer's first read, or the model's last norm (which then sees the sum of the copies).  Either does the
+    write and its own read in one launch."""
+
+    def __init__(self, rt, streams, x, y, mix, out_w):
+        self.rt, self.streams, self.x, self.y, self.mix, self.out_w = rt, streams, x, y, mix, out_w
+
+    def apply(self, h, gamma, eps, read_w=None, rows=None, u_out=None, write_streams=True):
+        ops.hc_step(self.streams, h, gamma, eps, y=self.y, mix=self.mix, out_w=self.out_w, read_w=read_w, rows=rows,
+                    u_out=u_out, write_streams=write_streams)
+
+    def materialize(self):
+        """Does the write, leaves the sum of the copies in the model's residual rows; nothing is left to add."""
+        self.apply(None, None, 0.0, u_out=self.x)
+        return None
+
+    def fused_add_rmsnorm(self, x, gamma, h, eps, rows, write_x, h32):
+        if h32 is not None:
+            self.materialize()
+            ops.add_rmsnorm(x, None, gamma, h, eps, rows=rows, write_x=False, h32=h32)
+            return
+        self.apply(h, gamma, eps, rows=rows, u_out=x if write_x else None, write_streams=write_x)
+
+
+class HyperConnectionBlock(Part):
+    """A pre-norm layer over several copies of the residual stream (see ``HyperConnectionBlockSpec``).  The copies
+    are float32 [streams, rows, width].  What lies between two sublayers is one launch: the write of the one that
+    ran (all copies at once from the old ones), the weighted read of the next and its RMS norm.  The stack's first
+    layer fills the copies from the rows it is given; the last layer's second write travels on to the model's last
+    norm, which reads the plain sum of the copies."""
+
+    graph_safe = True
+
+    def __init__(self, spec, rt):
+        self.spec, self.rt = spec, rt
+        if spec.streams > ops.HC_MAX_STREAMS or spec.streams < 1:
+            raise Unsupported("streams", f"{spec.streams}; the kernel takes 1 to {ops.HC_MAX_STREAMS} copies of the residual stream")
+        self.mixer_norm = build("norm", spec.mixer_norm, rt)
+        self.mixer = build("mixer", spec.mixer, rt)
+        self.ffn_norm = build("norm", spec.ffn_norm, rt)
+        self.ffn = build("ffn", spec.ffn, rt)
+        self.weights = {}
+
+    def children(self):
+        return [p for p in (self.mixer_norm, self.mixer, self.ffn_norm, self.ffn) if p is not None]
+
+    def _prefixes(self):
+        s = self.spec
+        return [s.mixer_prefix] + ([s.ffn_prefix] if s.ffn is not None else [])
+
+    def param_specs(self):
+        s, nm, S = self.spec, self.spec.names, self.spec.streams
+        specs = []
+        for p in self._prefixes():
+            specs += [ParamSpec(p + nm.read, (S,), "stream_read", init=(1.0 / S, 0.3 / S)),
+                      ParamSpec(p + nm.write, (S,), "stream_write", init=(1.0, 0.3)),
+                      ParamSpec(p + nm.mix, (S, S), "stream_mix", init=(0.0, 0.2))]
+        return specs
+
+    def allocate(self, stored, rt):
+        nm, S = self.spec.names, self.spec.streams
+        views = {}
+        for p in self._prefixes():
+            block = torch.empty(S * S + 2 * S, dtype=torch.float32, device=rt.device)
+            w = {"mix": block[:S * S].view(S, S), "read": block[S * S:S * S + S], "write": block[S * S + S:]}
+            self.weights[p] = w
+            views.update({p + nm.mix: w["mix"], p + nm.read: w["read"], p + nm.write: w["write"]})
+        return views
+
+    def forward(self, x, pending, ctx, layer):
+        rt, s = self.rt, self.spec
+        n = x.shape[0]
+        streams = rt.ws.get("residual_streams", (s.streams, n, s.hidden), torch.float32)
+        h = rt.ws.get("block_h", tuple(x.shape), rt.dtype)
+        w1 = self.weights[s.mixer_prefix]
+        gamma1, eps = self.mixer_norm.weight, s.mixer_norm.eps
+        if isinstance(pending, DeferredStreamWrite) and pending.streams.data_ptr() == streams.data_ptr() and s.index > 0:
+            pending.apply(h, gamma1, eps, read_w=w1["read"])
+        elif s.index == 0:
+            before = plain_delta(None, pending)
+            if before is not None:
+                x.add_(before)
+            ops.hc_step(streams, h, gamma1, eps, x0=x, read_w=w1["read"])          # every copy starts as x
+        else:
+            if pending is not None:
+                raise Backend("a layer over several residual streams was handed a result that is not a write into them")
+            ops.hc_step(streams, h, gamma1, eps, read_w=w1["read"], write_streams=False)
+        y = plain_delta(None, self.mixer.forward(h, ctx, layer))
+        last = w1
+        if self.ffn is not None:
+            w2 = self.weights[s.ffn_prefix]
+            ops.hc_step(streams, h, self.ffn_norm.weight, s.ffn_norm.eps, y=y, mix=w1["mix"], out_w=w1["write"], read_w=w2["read"])
+            y = plain_delta(None, self.ffn.forward(h, ctx))
+            last = w2
+        pending = DeferredStreamWrite(rt, streams, x, y, last["mix"], last["write"])
+        if "residual_trace" in ctx.aux:
+            # debugging aid (see ScaledDepthMixBlock._trace): the write is done here so that x is the layer's result
+            pending.materialize()
+            ctx.aux["residual_trace"].append(x.clone())
+            return None
+        return pending
+
+
 register("block", "prenorm_residual", PreNormResidualBlock)
+register("block", "hyper_connections", HyperConnectionBlock)
 register("block", "sandwich_residual", SandwichBlock)
 register("block", "prenorm_scaled_depthmix", ScaledDepthMixBlock)

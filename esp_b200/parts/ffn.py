@@ -123,6 +123,51 @@ class DenseXielu(Part):
         return y
 
 
+def glu_clamped_linear(rt, a, w_gate_up, act, spec, tag):
+    """act = g sigmoid(alpha g) (u + shift), g = min(a @ w_gate.T, limit), u = clamp(a @ w_up.T, -limit, limit), in the
+    activation dtype; w_gate_up is [2I, K] with the gate rows first."""
+    gu = rt.ws.get(tag + "_gu", (a.shape[0], w_gate_up.shape[0]), torch.float32)
+    linear(rt, a, w_gate_up, gu)
+    ops.glu_clamped(gu, act, spec.limit, spec.alpha, spec.up_shift)
+    return act
+
+
+class ClampedGlu(Part):
+    """y = W_d(g sigmoid(alpha g) (u + shift)) with g = min(W_g h, limit) and u = clamp(W_u h, -limit, limit), no biases:
+    a gated unit whose two branches are bounded before they meet."""
+
+    graph_safe = True
+
+    def __init__(self, spec, rt):
+        self.spec, self.rt = spec, rt
+        self.w_gate_up = self.w_down = None
+
+    def param_specs(self):
+        s, p, n = self.spec, self.spec.prefix, self.spec.names
+        return [ParamSpec(p + n.gate, (s.intermediate, s.hidden), "matrix"),
+                ParamSpec(p + n.up, (s.intermediate, s.hidden), "matrix"),
+                ParamSpec(p + n.down, (s.hidden, s.intermediate), "matrix")]
+
+    def allocate(self, stored, rt):
+        s, p, n = self.spec, self.spec.prefix, self.spec.names
+        dt = rt.matrix_dtype([stored[p + n.gate], stored[p + n.up]])
+        self.w_gate_up = torch.empty((2 * s.intermediate, s.hidden), dtype=dt, device=rt.device)
+        self.w_down = torch.empty((s.hidden, s.intermediate), dtype=rt.matrix_dtype([stored[p + n.down]]), device=rt.device)
+        return {p + n.gate: self.w_gate_up[:s.intermediate], p + n.up: self.w_gate_up[s.intermediate:], p + n.down: self.w_down}
+
+    def forward(self, h, ctx, h32=None):
+        rt, s = self.rt, self.spec
+        n = h.shape[0]
+        y = rt.ws.get("ffn_out", (n, s.hidden), torch.float32)
+        step = rt.ffn_chunk_tokens
+        for a in range(0, n, step):
+            b = min(n, a + step)
+            act = rt.ws.get("glu_act", (b - a, s.intermediate), rt.dtype)
+            glu_clamped_linear(rt, h[a:b], self.w_gate_up, act, s, "glu")
+            linear(rt, act, self.w_down, y[a:b])
+        return y
+
+
 class MoeSwiGluShared(Part):
     """Router (32-bit softmax over all experts, top-k, ties to the lower id,
     optional renormalisation), routed SwiGLU experts whose outputs are scaled
@@ -418,6 +463,7 @@ class ScaledInputMoe(Part):
 
 
 register("ffn", "swiglu", DenseSwiGlu)
+register("ffn", "glu_clamped", ClampedGlu)
 register("ffn", "moe_sigmoid_scaled_input", ScaledInputMoe)
 register("ffn", "xielu", DenseXielu)
 register("ffn", "moe_swiglu_shared", MoeSwiGluShared)
