@@ -498,6 +498,28 @@ def sparse_qwen2_config(width, ff, layers, vocab):
                 mlp_only_layers=list(range(0, layers, 2)), max_position_embeddings=8192)
 
 
+# --design migosun: the decoder whose layers run chunked attention with learned sinks beside the delta rule, or gated
+# linear attention, over several copies of the residual stream, beside the Zusepel decoder of the same width, depth and
+# feed-forward width (the closest model this library has: matrix-state recurrences with a decay per key channel,
+# attention behind a mask, dense gated feed-forwards).  The recurrences have as many heads of 128 x 128 as Zusepel's;
+# the attention has heads of 128 with a key head to four query heads and a chunk as long as Zusepel's window.
+def migosun_config(width, ff, layers, vocab, window):
+    heads = width // 128
+    par = {"left": {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+                    "rot": {"dims": 64, "base": 10000.0}, "mask": {"size": window}},
+           "right": {"heads": heads, "kv_heads": heads, "dim": 128, "vdim": 128, "conv": 4},
+           "left_scale": 1.0, "right_scale": 1.0}
+    gla = {"heads": heads, "dim": 128, "vdim": 128, "tau": 16.0}
+    out = [{"type": "gla" if i % 4 == 3 else "parallel", "mixer": dict(gla) if i % 4 == 3 else dict(par),
+            "mlp": {"kind": "dense", "ff": ff, "limit": 7.0}} for i in range(layers)]
+    ranks = {}
+    for i, layer in enumerate(out):
+        for name in (("a1",) if layer["type"] == "gla" else ("a1", "g1")):
+            ranks[f"{i}:{name}"] = 64
+    return {"architecture": "Migosun", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "embedding": {"scale": 1.0},
+            "streams": 2, "layers": out, "ranks": ranks}
+
+
 def measure_design(torch, raw, prefill_tokens, batches, context, steps, warmup, clocks):
     """Prefill of one prompt and decode steps of a model with random weights: tokens per second, and device time
     by kind of kernel for one eager prefill and one eager decode step (library products count with the kernel
@@ -554,8 +576,9 @@ def bench_design(torch, a, pk):
     sizes = {"w1024": (1024, 2816, 8), "w2048": (2048, 5632, 8), "w4096": (4096, 11008, 8)}
     picked = [s for s in a.design_sizes.split(",") if s]
     vocab, window = 32768, 4096
-    vumedra = a.design == "vumedra"
+    vumedra, migosun = a.design == "vumedra", a.design == "migosun"
     beside = ("Qwen2 MoE decoder of equal width, depth, heads, dense and expert sizes" if vumedra else
+              "Zusepel decoder of equal width, depth and feed-forward width" if migosun else
               "dense Qwen2 decoder of equal width, depth and feed-forward width")
     result = {"design": a.design, "beside": beside, "dtype": "bf16",
               "data": "synthetic token ids, random weights N(0,0.02)", "prefill_tokens": a.prefill_tokens,
@@ -564,11 +587,15 @@ def bench_design(torch, a, pk):
     for name in picked:
         width, ff, layers = sizes[name]
         entry = {"width": width, "ff": ff, "layers": layers, "vocab": vocab}
-        mine = vumedra_config(width, ff, layers, vocab) if vumedra else zusepel_config(width, ff, layers, vocab, window)
-        other = sparse_qwen2_config(width, ff, layers, vocab) if vumedra else dense_qwen2_config(width, ff, layers, vocab)
+        if migosun:
+            mine, other = migosun_config(width, ff, layers, vocab, window), zusepel_config(width, ff, layers, vocab, window)
+        elif vumedra:
+            mine, other = vumedra_config(width, ff, layers, vocab), sparse_qwen2_config(width, ff, layers, vocab)
+        else:
+            mine, other = zusepel_config(width, ff, layers, vocab, window), dense_qwen2_config(width, ff, layers, vocab)
         entry[a.design] = measure_design(torch, mine, a.prefill_tokens, (1, 8), a.context, a.steps, a.warmup, clocks)
-        entry["qwen2_moe" if vumedra else "qwen2_dense"] = measure_design(torch, other, a.prefill_tokens, (1, 8), a.context,
-                                                                          a.steps, a.warmup, clocks)
+        entry["zusepel" if migosun else "qwen2_moe" if vumedra else "qwen2_dense"] = measure_design(
+            torch, other, a.prefill_tokens, (1, 8), a.context, a.steps, a.warmup, clocks)
         result["sizes"][name] = entry
     result["clocks"] = clocks.summary()
     print(json.dumps(result))
@@ -577,9 +604,10 @@ def bench_design(torch, a, pk):
 
 def main() -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--design", default=None, choices=["zusepel", "vumedra"],
+    ap.add_argument("--design", default=None, choices=["zusepel", "vumedra", "migosun"],
                     help="instead of the default workload: prefill and decode of this design at a few layer sizes, beside "
-                         "the closest Qwen2 decoder of equal size (dense for zusepel, with routed experts for vumedra)")
+                         "the closest other decoder of equal size (the dense Qwen2 for zusepel, the Qwen2 with routed "
+                         "experts for vumedra, zusepel for migosun)")
     ap.add_argument("--design-sizes", default="w1024,w2048", help="with --design: which of w1024, w2048, w4096")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=32)

@@ -91,7 +91,7 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
                       int* __restrict__ counters, const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
                       const int* __restrict__ seq_past, const int* __restrict__ block_table, int table_stride, int n_pages,
                       int page, int nh, int nkv, int window, int split_keys, int n_splits, float score_scale, int sink,
-                      int* __restrict__ status) {
+                      const float* __restrict__ sink_vals, int chunk, int* __restrict__ status) {
     pdl_trigger();
     constexpr int ITEM = PAGE_KEYS * HD;
     constexpr int NBW = HD / 32;                   // 8-column blocks of the head that one warp accumulates
@@ -110,7 +110,7 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
     const int kvh = blockIdx.y / blocks_per_kv, h0 = kvh * group + (blockIdx.y % blocks_per_kv) * MMA_HEADS;
     const int heads = min(MMA_HEADS, (kvh + 1) * group - h0);
     const int pos = tok_pos[n], seq = tok_seq[n];
-    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    const int lo = first_visible_key(pos, window, chunk);
     const int j0 = max(lo, split * split_keys), j1 = min(pos, split * split_keys + split_keys - 1);
     if (j0 > j1) return;
     const int first_page = j0 / PAGE_KEYS, n_pg = j1 / PAGE_KEYS - first_page + 1, n_items = 2 * n_pg;
@@ -318,8 +318,10 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
         for (int sp = s0 + lane; sp <= s1; sp += 32) mx = fmaxf(mx, __ldcg(ml + 2 * sp));
 #pragma unroll
         for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
-        if (sink) mx = fmaxf(mx, 0.f);                     // one more key of score zero, without a value
-        float denom = sink ? expf(-mx) : 0.f, num[NV][2];
+        // one more key without a value, of score zero or of the head's own score
+        const float sink_score = sink && sink_vals ? sink_vals[h0 + g] : 0.f;
+        if (sink) mx = fmaxf(mx, sink_score);
+        float denom = sink ? expf(sink_score - mx) : 0.f, num[NV][2];
 #pragma unroll
         for (int j = 0; j < NV; j++) num[j][0] = num[j][1] = 0.f;
         for (int c0 = s0; c0 <= s1; c0 += WCH) {
@@ -381,7 +383,8 @@ int make_cache_map(CUtensorMap* map, const void* base, unsigned long long rows, 
 template <int HD>
 int launch_split_mma(int split, const bf16* q, const bf16* k, const bf16* v, bf16* out, float* po, float* pml, int* counters,
                      const int* tok_seq, const int* tok_pos, const int* seq_past, const int* table, int stride, int n_pages, int page,
-                     int n_tokens, int nh, int nkv, int window, int n_splits, float score_scale, int sink, int* status,
+                     int n_tokens, int nh, int nkv, int window, int n_splits, float score_scale, int sink,
+                     const float* sink_vals, int chunk, int* status,
                      cudaStream_t stream) {
     CUtensorMap map_k, map_v;
     const unsigned long long rows = (unsigned long long)n_pages * nkv * PAGE_KEYS;
@@ -402,7 +405,7 @@ int launch_split_mma(int split, const bf16* q, const bf16* k, const bf16* v, bf1
     dim3 grid(n_tokens, nkv * ((group + MMA_HEADS - 1) / MMA_HEADS), n_splits);
     esp_launch_pdl(ESP_PDL_ATTENTION, attn_split_mma_kernel<HD>, dim3(grid), dim3(THREADS), dyn, stream, map_k, map_v, q, out, po, pml,
                    counters, tok_seq, tok_pos, seq_past, table, stride, n_pages, page, nh, nkv, window, split, n_splits, score_scale,
-                   sink, status);
+                   sink, sink_vals, chunk, status);
     return esp_launch_status();
 }
 }  // namespace
@@ -418,15 +421,15 @@ int launch_split_mma(int split, const bf16* q, const bf16* k, const bf16* v, bf1
 ESP_API int esp_attn_decode(const void* q, const void* k_cache, const void* v_cache, void* out, float* part_o,
                             float* part_ml, int* counters, const int* tok_seq, const int* tok_pos, const int* seq_past,
                             const int* block_table, int table_stride, int n_pages, int page, int n_tokens, int nh, int nkv,
-                            int hd, int window, int split, int n_splits, float score_scale, int sink, int* status,
-                            cudaStream_t stream) {
+                            int hd, int window, int split, int n_splits, float score_scale, int sink, const float* sink_vals,
+                            int chunk, int* status, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (nkv <= 0 || nh % nkv != 0 || n_splits <= 0 || n_splits > 65535 || nh > 65535 || split < PAGE_KEYS || split % PAGE_KEYS != 0 ||
         page != PAGE_KEYS)
         return (int)cudaErrorInvalidValue;
 #define ESP_HD(HD) return launch_split_mma<HD>(split, (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, (bf16*)out, part_o, \
                                                part_ml, counters, tok_seq, tok_pos, seq_past, block_table, table_stride, n_pages, \
-                                               page, n_tokens, nh, nkv, window, n_splits, score_scale, sink, status, stream)
+                                               page, n_tokens, nh, nkv, window, n_splits, score_scale, sink, sink_vals, chunk, status, stream)
     switch (hd) {
         case 64: ESP_HD(64);
         case 128: ESP_HD(128);
@@ -483,5 +486,5 @@ extern "C" int esp_attn_decode_noalloc(const void* q, const void* k_cache, const
     float* part_ml = part_o + (size_t)n_tokens * nh * n_splits * hd;
     int* counters = reinterpret_cast<int*>(noalloc_scratch_of_device[device] + esp_attn_decode_noalloc_capacity());
     return esp_attn_decode(q, k_cache, v_cache, out, part_o, part_ml, counters, tok_seq, tok_pos, nullptr, block_table, table_stride,
-                           n_pages, page, n_tokens, nh, nkv, hd, window, split, n_splits, 0.f, 0, status, stream);
+                           n_pages, page, n_tokens, nh, nkv, hd, window, split, n_splits, 0.f, 0, nullptr, 0, status, stream);
 }

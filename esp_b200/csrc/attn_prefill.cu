@@ -54,7 +54,8 @@ attn_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache
                     bf16* __restrict__ out, const int* __restrict__ tile_seq, const int* __restrict__ tile_first,
                     const int* __restrict__ seq_start, const int* __restrict__ seq_past,
                     const int* __restrict__ block_table, int table_stride, int n_pages, int nh, int nkv, int hd,
-                    int vd, float scale, int sink, int window, int* __restrict__ status) {
+                    int vd, float scale, int sink, const float* __restrict__ sink_vals, int window, int chunk,
+                    int* __restrict__ status) {
     constexpr int LDS = HDK + 8;                     // row stride in elements: 16 bytes of padding against bank conflicts
     constexpr int LDV = HDV + 8;
     constexpr int PIECES = HDK / 8, VPIECES = HDV / 8;
@@ -85,7 +86,7 @@ attn_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache
     }
     cp_async_commit();
 
-    const int key_lo = window > 0 ? max(0, pos0 - window + 1) : 0;     // first key any row of the tile sees
+    const int key_lo = first_visible_key(pos0, window, chunk);         // first key any row of the tile sees
     const int blk_lo = key_lo / BN, blk_hi = pos_last / BN;
 
     auto load_kv = [&](int blk, int buf) {
@@ -126,13 +127,15 @@ attn_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache
 #pragma unroll
         for (int j = 0; j < 4; j++) o[i][j] = 0.f;
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
-    if (sink) {
-        m_run[0] = m_run[1] = 0.f;
+    if (sink) {                                      // a key of score zero, or of the head's own score, without a value
+        m_run[0] = m_run[1] = sink_vals ? sink_vals[h] : 0.f;
         if (tg == 0) l_run[0] = l_run[1] = 1.f;      // the sums of a row's four lanes are added at the end: one of them holds the sink
     }
     const float root = sqrtf((float)hd);
     const float log2e = 1.4426950408889634f;
     const int my_pos[2] = {pos0 + warp * 16 + g, pos0 + warp * 16 + g + 8};   // absolute positions of this lane's two rows
+    const int my_first[2] = {first_visible_key(my_pos[0], window, chunk), first_visible_key(my_pos[1], window, chunk)};
+    const int warp_first = first_visible_key(pos0 + warp * 16 + 15, window, chunk);   // of the warp's last row
 
     for (int blk = blk_lo; blk <= blk_hi; blk++) {
         const int buf = (blk - blk_lo) & 1;
@@ -161,7 +164,7 @@ attn_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache
         // scale, mask, running maximum
         const int key0 = blk * BN;
         // does any (row of this warp, key of this block) pair need the mask?
-        const bool edge = key0 + BN - 1 > pos0 + warp * 16 || (window > 0 && key0 < pos0 + warp * 16 + 15 - window + 1);
+        const bool edge = key0 + BN - 1 > pos0 + warp * 16 || key0 < warp_first;
         float m_new[2] = {m_run[0], m_run[1]};
 #pragma unroll
         for (int nb = 0; nb < BN / 8; nb++) {
@@ -171,7 +174,7 @@ attn_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache
                 const int key = key0 + nb * 8 + tg * 2 + (j & 1);
                 float v = scale > 0.f ? s[nb][j] * scale : s[nb][j] / root;
                 if (edge) {
-                    const bool seen = key <= my_pos[r] && (window <= 0 || my_pos[r] - key < window);
+                    const bool seen = key <= my_pos[r] && key >= my_first[r];
                     if (!seen) v = -INFINITY;
                 }
                 s[nb][j] = v;
@@ -251,7 +254,8 @@ attn_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache
 template <int HDK, int HDV>
 int launch(const bf16* q, const bf16* k, const bf16* v, bf16* out, const int* tile_seq, const int* tile_first,
            const int* seq_start, const int* seq_past, const int* table, int stride, int n_pages, int n_tiles, int nh,
-           int nkv, int hd, int vd, float scale, int sink, int window, int* status, cudaStream_t stream) {
+           int nkv, int hd, int vd, float scale, int sink, const float* sink_vals, int window, int chunk, int* status,
+           cudaStream_t stream) {
     static_assert(BM <= BN, "the queries borrow a key buffer");
     const size_t smem = (size_t)(2 * BN) * ((HDK + 8) + (HDV + 8)) * sizeof(bf16);
     static bool raised = false;
@@ -263,7 +267,7 @@ int launch(const bf16* q, const bf16* k, const bf16* v, bf16* out, const int* ti
     dim3 grid(n_tiles, nh);
     attn_prefill_kernel<HDK, HDV><<<grid, THREADS, smem, stream>>>(q, k, v, out, tile_seq, tile_first, seq_start, seq_past,
                                                                    table, stride, n_pages, nh, nkv, hd, vd, scale, sink,
-                                                                   window, status);
+                                                                   sink_vals, window, chunk, status);
     return esp_launch_status();
 }
 }  // namespace
@@ -274,7 +278,8 @@ int launch(const bf16* q, const bf16* k, const bf16* v, bf16* out, const int* ti
 ESP_API int esp_attn_prefill(const void* q, const void* k_cache, const void* v_cache, void* out, const int* tile_seq,
                              const int* tile_first, const int* seq_start, const int* seq_past, const int* block_table,
                              int table_stride, int n_pages, int page, int n_tiles, int nh, int nkv, int hd, int vd,
-                             float scale, int sink, int window, int* status, cudaStream_t stream) {
+                             float scale, int sink, const float* sink_vals, int window, int chunk, int* status,
+                             cudaStream_t stream) {
     if (n_tiles <= 0) return 0;
     if (vd <= 0) vd = hd;
     if (page != BN || hd % 8 != 0 || hd > 128 || hd <= 0 || vd % 8 != 0 || vd > 128 || nkv <= 0 || nh % nkv != 0 || nh > 65535)
@@ -282,7 +287,7 @@ ESP_API int esp_attn_prefill(const void* q, const void* k_cache, const void* v_c
 #define ESP_FLASH(HDK_, HDV_)                                                                                              \
     return launch<HDK_, HDV_>((const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, (bf16*)out, tile_seq, tile_first, \
                               seq_start, seq_past, block_table, table_stride, n_pages, n_tiles, nh, nkv, hd, vd, scale, sink, \
-                              window, status, stream)
+                              sink_vals, window, chunk, status, stream)
     if (hd <= 64 && vd <= 64) ESP_FLASH(64, 64);
     if (hd <= 64) ESP_FLASH(64, 128);
     if (vd <= 64) ESP_FLASH(128, 64);

@@ -52,6 +52,8 @@ struct AttnParams {
     int* status;
     float scale;      // > 0: multiplies the scores; else they are divided by sqrt(head size)
     int sink;         // the softmax's denominator holds one more term, a key of score zero without a value
+    const float* sink_vals;   // with sink: the term is exp(sink_vals[head]) instead (a number per head, not scaled); may be null
+    int chunk;        // > 0: a query sees the keys of its own block of ``chunk`` positions (counted from 0) only
 };
 
 // instruction descriptor: bfloat16 x bfloat16 -> float, M = 128, N = n, A K-major, B K-major or MN-major
@@ -94,7 +96,7 @@ __device__ __forceinline__ void named_sync(int id, int count) {
 
 // the tile of 128 query rows and the head that a block works on
 struct Item {
-    int seq, h, kvh, row0, rows, pos0, pos_last, blk_lo, nb;
+    int seq, h, kvh, row0, rows, pos0, pos_last, blk_lo, nb, page_lo;
 };
 __device__ __forceinline__ Item load_item(const AttnParams& p, int item) {
     Item it;
@@ -107,8 +109,9 @@ __device__ __forceinline__ Item load_item(const AttnParams& p, int item) {
     it.rows = min(BM, p.seq_start[it.seq + 1] - p.seq_start[it.seq] - first);
     it.pos0 = p.seq_past[it.seq] + first;
     it.pos_last = it.pos0 + it.rows - 1;
-    const int key_lo = p.window > 0 ? max(0, it.pos0 - p.window + 1) : 0;
+    const int key_lo = first_visible_key(it.pos0, p.window, p.chunk);
     it.blk_lo = key_lo / BN;
+    it.page_lo = key_lo / PAGE;                                          // the first page that holds a key any row sees
     it.nb = it.pos_last / BN - it.blk_lo + 1;
     return it;
 }
@@ -205,10 +208,11 @@ attn_prefill_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             for (int j = 0; j < t.nb && ok; j++, g++) {
                 const int s = g % STAGES, ph = (g / STAGES) & 1;
                 if ((j & 15) == 0) {
-                    // a page past the tile's last key is read as zeros (a row past the cache)
+                    // a page past the tile's last key, or ahead of the first key that any of its rows sees (the sequence
+                    // may have given it back), is read as zeros (a row past the cache)
                     rows16 = p.kv_rows;
                     const int page_idx = (t.blk_lo + j) * 2 + lane;
-                    if (page_idx <= t.pos_last / PAGE) {
+                    if (page_idx <= t.pos_last / PAGE && page_idx >= t.page_lo) {
                         const int pg = p.block_table[(size_t)t.seq * p.table_stride + page_idx];
                         if (pg >= 0 && pg < p.n_pages) rows16 = (pg * p.nkv + t.kvh) * PAGE;
                         else atomicOr(p.status, ESP_STATUS_BAD_INDEX);
@@ -320,7 +324,9 @@ attn_prefill_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             if (item >= n_items) break;
             const Item t = load_item(p, item);
             const int pos = t.pos0 + r;
-            const int key_first = p.window > 0 ? pos - p.window + 1 : 0; // the keys this row sees: key_first .. pos
+            // the keys this row sees: key_first .. pos (a window's first key may lie before the sequence's start)
+            const int key_first = p.chunk > 0 ? pos - pos % p.chunk : (p.window > 0 ? pos - p.window + 1 : 0);
+            const int key_first_last = first_visible_key(t.pos0 + BM - 1, p.window, p.chunk);   // of the tile's last row
             float m_ref = -INFINITY, l_run = 0.f;                         // the maximum that O and l_run are scaled by
             for (int j = grp; j < t.nb && ok; j += GROUPS, n_b++) {
                 const int key0 = (t.blk_lo + j) * BN;
@@ -330,7 +336,7 @@ attn_prefill_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 // S is done, and so are the products issued before it: the group's O holds its blocks so far
                 tc_fence_after();
                 // does any (row of the tile, key of the block) pair need the mask?
-                const bool edge = key0 + BN - 1 > t.pos0 || (p.window > 0 && key0 < t.pos0 + BM - 1 - p.window + 1);
+                const bool edge = key0 + BN - 1 > t.pos0 || key0 < key_first_last;
                 // live columns of this row: c_lo .. c_lo + c_span; one unsigned comparison per element, no branch
                 const int c_lo = key_first - key0 - side * CW;
                 const unsigned c_span = (unsigned)(pos - key_first);
@@ -420,14 +426,16 @@ attn_prefill_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             float m_all = -INFINITY, f[GROUPS], l_all = 0.f;
 #pragma unroll
             for (int b = 0; b < GROUPS; b++) m_all = fmaxf(m_all, xchg[b * (ROWT * 128) + 128 + r]);
-            if (p.sink) m_all = fmaxf(m_all, 0.f);                        // the sink's score is zero
+            // the sink's score is zero, or the head's own number (in the units of the maxima: times log2 e)
+            const float sink2 = p.sink && p.sink_vals ? p.sink_vals[t.h] * 1.4426950408889634f : 0.f;
+            if (p.sink) m_all = fmaxf(m_all, sink2);
 #pragma unroll
             for (int b = 0; b < GROUPS; b++) {                            // a group without a key for this row counts 0
                 const float m_b = xchg[b * (ROWT * 128) + 128 + r];
                 f[b] = m_b == -INFINITY ? 0.f : fast_exp2(m_b - m_all);
                 l_all += f[b] * xchg[b * (ROWT * 128) + r];
             }
-            if (p.sink) l_all += fast_exp2(-m_all);
+            if (p.sink) l_all += fast_exp2(sink2 - m_all);
             const float inv = l_all > 0.f ? 1.0f / l_all : 0.f;
             const int col0 = (grp * ROWT + side) * FW;
             float o[FW];
@@ -534,7 +542,8 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, 
 ESP_API int esp_attn_prefill_tc05(const void* q, long long n_tokens, const void* k_cache, const void* v_cache, void* out,
                                   const int* tile_seq, const int* tile_first, const int* seq_start, const int* seq_past,
                                   const int* block_table, int table_stride, int n_pages, int page, int n_tiles, int nh,
-                                  int nkv, int hd, float scale, int sink, int window, int* status, cudaStream_t stream) {
+                                  int nkv, int hd, float scale, int sink, const float* sink_vals, int window, int chunk, int* status,
+                                  cudaStream_t stream) {
     if (n_tiles <= 0) return 0;
     if (page != PAGE || (hd != 64 && hd != 128) || nkv <= 0 || nh % nkv != 0 || nh > 65535 || n_tokens <= 0)
         return (int)cudaErrorInvalidValue;
@@ -548,7 +557,7 @@ ESP_API int esp_attn_prefill_tc05(const void* q, long long n_tokens, const void*
     rc = make_map2d(&mv, v_cache, (unsigned long long)hd, kv_rows, PAGE);
     if (rc) return rc;
     AttnParams p{(bf16*)out, tile_seq, tile_first, seq_start, seq_past, block_table, table_stride, n_pages, nh, nkv,
-                 window, (int)kv_rows, n_tiles, 0, status, scale, sink};
+                 window, (int)kv_rows, n_tiles, 0, status, scale, sink, sink_vals, chunk};
     if (hd == 64) return launch<64>(mq, mk, mv, p, n_tiles, stream);
     return launch<128>(mq, mk, mv, p, n_tiles, stream);
 }

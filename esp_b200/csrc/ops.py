@@ -85,11 +85,11 @@ _SIGNATURES = {
     "esp_qkv_rope_skinny": [P, c_longlong, P, P, P, P, P, P, c_int, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int,
                             c_int, c_int, c_int, P, P],
     "esp_attn_prefill": [P, P, P, P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
-                         c_int, P, P],
+                         P, c_int, c_int, P, P],
     "esp_attn_prefill_tc05": [P, c_longlong, P, P, P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
-                              c_int, c_int, P, P],
+                              c_int, P, c_int, c_int, P, P],
     "esp_attn_decode": [P, P, P, P, P, P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                        c_int, c_float, c_int, P, P],
+                        c_int, c_float, c_int, P, c_int, P, P],
 }
 
 _bound: dict = {}
@@ -575,14 +575,16 @@ ATTN_DECODE_COUNTERS = 65536
 
 
 def attn_decode(q, k_cache, v_cache, out, part_o, part_ml, counters, tok_seq, tok_pos, block_table, page, nh, nkv, hd,
-                window, split, n_splits, status, seq_past=None, scale=0.0, sink=False):
+                window, split, n_splits, status, seq_past=None, scale=0.0, sink=False, chunk=None):
     """Split-key attention for few token rows (bfloat16; head sizes 64, 128, 192, 256).  ``split``: key
     positions per block (a multiple of 64); n_splits >= ceil(positions / split).  part_o float32
     [N, nh, n_splits, hd] and part_ml float32 [N, nh, n_splits, 2] are scratch; ``counters``: int32, at least
     N * nh words, all zero (the kernel leaves them zero).  ``seq_past`` (int32 per sequence of the step: the
     positions cached before it): blocks whose keys are all older then load them without waiting for the
     kernel before this one, which writes the step's new keys and values.  ``scale`` > 0 multiplies the scores instead
-    of the division by sqrt(hd); ``sink``: the softmax's denominator holds one more term exp(0)."""
+    of the division by sqrt(hd); ``sink``: the softmax's denominator holds one more term exp(0), or exp(sink[head]) when
+    a float32 tensor is given; ``chunk``: a query sees the keys of its own block of that many positions only."""
+    sink_flag, sink_ptr = _sink_args(sink, nh)
     if counters.numel() < q.shape[0] * nh:
         raise Backend("attn_decode: too few counters for this many rows and heads")
     if split < 64 or split % 64:
@@ -597,8 +599,8 @@ def attn_decode(q, k_cache, v_cache, out, part_o, part_ml, counters, tok_seq, to
         _ptr(out, torch.bfloat16), _ptr(part_o, torch.float32), _ptr(part_ml, torch.float32),
         _ptr(counters, torch.int32), _ptr(tok_seq, torch.int32), _ptr(tok_pos, torch.int32), _ptr(seq_past, torch.int32),
         _ptr(block_table, torch.int32), block_table.shape[1],
-        k_cache.shape[0], page, n, nh, nkv, hd, int(window or 0), split, n_splits, float(scale), 1 if sink else 0,
-        _ptr(status, torch.int32), _stream()), "attn_decode")
+        k_cache.shape[0], page, n, nh, nkv, hd, int(window or 0), split, n_splits, float(scale), sink_flag, sink_ptr,
+        int(chunk or 0), _ptr(status, torch.int32), _stream()), "attn_decode")
 
 
 def attn_flash_fits(hd, vd=None, page=64) -> bool:
@@ -608,11 +610,13 @@ def attn_flash_fits(hd, vd=None, page=64) -> bool:
 
 
 def attn_prefill(q, k_cache, v_cache, out, tile_seq, tile_first, seq_start, seq_past, block_table, page, nh, nkv, hd,
-                 window, status, vd=None, scale=0.0, sink=False):
+                 window, status, vd=None, scale=0.0, sink=False, chunk=None):
     """Flash-style attention for runs of new tokens (bfloat16; head sizes that are multiples of 8 up to
     128; pages of 64 positions).  tile_seq / tile_first describe the tiles of 64 new tokens.  ``vd``: size of a
     value head (default: the key size); ``scale`` > 0 multiplies the scores instead of the division by sqrt(hd);
-    ``sink``: the softmax's denominator holds one more term exp(0)."""
+    ``sink``: the softmax's denominator holds one more term exp(0), or exp(sink[head]) when a float32 tensor is given;
+    ``chunk``: a query sees the keys of its own block of that many positions only."""
+    sink_flag, sink_ptr = _sink_args(sink, nh)
     vd = hd if vd is None else vd
     if not attn_flash_fits(hd, vd, page):
         raise Backend(f"attn_prefill: head sizes {hd} / {vd} / page {page} not taken (multiples of 8 up to 128; page 64)")
@@ -620,8 +624,8 @@ def attn_prefill(q, k_cache, v_cache, out, tile_seq, tile_first, seq_start, seq_
         _ptr(q, torch.bfloat16, "q"), _ptr(k_cache, torch.bfloat16), _ptr(v_cache, torch.bfloat16),
         _ptr(out, torch.bfloat16), _ptr(tile_seq, torch.int32), _ptr(tile_first, torch.int32),
         _ptr(seq_start, torch.int32), _ptr(seq_past, torch.int32), _ptr(block_table, torch.int32),
-        block_table.shape[1], k_cache.shape[0], page, tile_seq.shape[0], nh, nkv, hd, vd, float(scale), 1 if sink else 0,
-        int(window or 0), _ptr(status, torch.int32), _stream()), "attn_prefill")
+        block_table.shape[1], k_cache.shape[0], page, tile_seq.shape[0], nh, nkv, hd, vd, float(scale), sink_flag, sink_ptr,
+        int(window or 0), int(chunk or 0), _ptr(status, torch.int32), _stream()), "attn_prefill")
 
 
 ATTN_TC05_TILE_ROWS = 128      # new tokens of a sequence to a tile of attn_prefill_tc05
@@ -633,12 +637,14 @@ def attn_prefill_tc05_fits(hd, page) -> bool:
 
 
 def attn_prefill_tc05(q, k_cache, v_cache, out, tile_seq, tile_first, seq_start, seq_past, block_table, page, nh, nkv, hd,
-                      window, status, scale=0.0, sink=False):
+                      window, status, scale=0.0, sink=False, chunk=None):
     """Prefill attention on tcgen05 with accumulators in tensor memory (bfloat16; head size 64 or 128; pages
     of 64 positions).  Same arguments as attn_prefill, but tile_seq / tile_first list tiles of
     ATTN_TC05_TILE_ROWS new tokens, best with the tiles that see the most keys first (the order only matters
     for the balance).  ``scale`` > 0 multiplies the scores instead of the division by sqrt(hd); ``sink``: the softmax's
-    denominator holds one more term exp(0)."""
+    denominator holds one more term exp(0), or exp(sink[head]) when a float32 tensor is given; ``chunk``: a query sees the
+    keys of its own block of that many positions only."""
+    sink_flag, sink_ptr = _sink_args(sink, nh)
     if not attn_prefill_tc05_fits(hd, page):
         raise Backend(f"attn_prefill_tc05: head size {hd} / page {page} not taken (64 or 128; page 64)")
     if not q.is_contiguous() or q.numel() != q.shape[0] * nh * hd:
@@ -647,8 +653,8 @@ def attn_prefill_tc05(q, k_cache, v_cache, out, tile_seq, tile_first, seq_start,
         _ptr(q, torch.bfloat16, "q"), q.shape[0], _ptr(k_cache, torch.bfloat16), _ptr(v_cache, torch.bfloat16),
         _ptr(out, torch.bfloat16), _ptr(tile_seq, torch.int32), _ptr(tile_first, torch.int32),
         _ptr(seq_start, torch.int32), _ptr(seq_past, torch.int32), _ptr(block_table, torch.int32),
-        block_table.shape[1], k_cache.shape[0], page, tile_seq.shape[0], nh, nkv, hd, float(scale), 1 if sink else 0,
-        int(window or 0), _ptr(status, torch.int32), _stream()), "attn_prefill_tc05")
+        block_table.shape[1], k_cache.shape[0], page, tile_seq.shape[0], nh, nkv, hd, float(scale), sink_flag, sink_ptr,
+        int(window or 0), int(chunk or 0), _ptr(status, torch.int32), _stream()), "attn_prefill_tc05")
 
 
 def gather_rows(src, rows, out):

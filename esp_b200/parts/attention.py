@@ -16,6 +16,73 @@ from .position import NoPosition
 DECODE_ROWS = 128      # steps with at most this many token rows use the split-key kernel
 
 
+# ---- attention with the scores' scale given, keys and values of different sizes, a sink, a window or a mask of blocks:
+# which kernel a step of n token rows gets, the index lists it needs, and the launch.  Shared by the parts below.
+def scaled_kernel_for(rt, key_dim: int, value_dim: int, scale: float, n: int, page: int = PAGE) -> str:
+    if rt.dtype == torch.bfloat16 and page == PAGE:
+        same = key_dim == value_dim and scale > 0
+        if same and key_dim in (64, 128, 192, 256) and n <= DECODE_ROWS:
+            return "split"         # few rows: the keys are split over blocks
+        if same and ops.attn_prefill_tc05_fits(key_dim, page):
+            return "tc05"          # many rows: scores and weighted values in tensor memory
+        if ops.attn_flash_fits(key_dim, value_dim):
+            return "flash"         # keys and values of different sizes, any multiples of 8 up to 128
+    return "plain"
+
+
+def scaled_tiles(kind: str, step) -> dict:
+    """Tiles of new tokens for the two tensor-core kernels of many rows: (sequence, first new token) per tile; for
+    the tensor-memory kernel the tiles that see the most keys come first (its blocks take them in order)."""
+    if kind == "tc05":
+        rows = ops.ATTN_TC05_TILE_ROWS
+        tiles = sorted(((i, f) for i, t in enumerate(step.news) for f in range(0, t, rows)),
+                       key=lambda sf: -(step.pasts[sf[0]] + min(sf[1] + rows, step.news[sf[0]])))
+    elif kind == "flash":
+        rows = 64
+        tiles = [(i, f) for i, t in enumerate(step.news) for f in range(0, t, rows)]
+    else:
+        return {}
+    return {f"attention.tiles{rows}.seq": np.asarray([t[0] for t in tiles], dtype=np.int32),
+            f"attention.tiles{rows}.first": np.asarray([t[1] for t in tiles], dtype=np.int32)}
+
+
+def scaled_attend(rt, kind, q, o, ctx, layer, num_heads, num_kv_heads, key_dim, value_dim, scale, sink, window=None, chunk=None):
+    """``sink``: False, True (a term exp(0)) or a float32 tensor with a number per head (a term exp(sink_h))."""
+    n = q.shape[0]
+    table = ctx.block_tables[layer.group]
+    tile_seq = tile_first = None
+    if kind in ("tc05", "flash"):
+        rows = ops.ATTN_TC05_TILE_ROWS if kind == "tc05" else 64
+        tile_seq, tile_first = ctx.arrays.get(f"attention.tiles{rows}.seq"), ctx.arrays.get(f"attention.tiles{rows}.first")
+        if tile_seq is None:
+            kind = "plain"         # a step made without this part's lists
+    if kind == "split":
+        positions = table.shape[1] * layer.page
+        group = num_heads // num_kv_heads
+        kv_blocks = num_kv_heads * ((group + 15) // 16)
+        # a layer with a window or a mask of blocks reads at most that many keys (+ a page) of each row
+        seen = window or chunk
+        span = min(positions, seen + layer.page) if seen else positions
+        split = ops.attn_decode_split(n, kv_blocks, span, key_dim, rt.sm_count)
+        n_splits = (positions + split - 1) // split
+        part_o = rt.ws.get("attn_part_o", (n, num_heads, n_splits, key_dim), torch.float32)
+        part_ml = rt.ws.get("attn_part_ml", (n, num_heads, n_splits, 2), torch.float32)
+        if getattr(rt, "attn_counters", None) is None:
+            rt.attn_counters = torch.zeros(ops.ATTN_DECODE_COUNTERS, dtype=torch.int32, device=rt.device)
+        ops.attn_decode(q, layer.k, layer.v, o, part_o, part_ml, rt.attn_counters, ctx.tok_seq, ctx.tok_pos, table, layer.page,
+                        num_heads, num_kv_heads, key_dim, window, split, n_splits, rt.status,
+                        seq_past=ctx.seq_past if layer.writes else None, scale=scale, sink=sink, chunk=chunk)
+    elif kind == "tc05":
+        ops.attn_prefill_tc05(q, layer.k, layer.v, o, tile_seq, tile_first, ctx.seq_start, ctx.seq_past, table, layer.page,
+                              num_heads, num_kv_heads, key_dim, window, rt.status, scale=scale, sink=sink, chunk=chunk)
+    elif kind == "flash":
+        ops.attn_prefill(q, layer.k, layer.v, o, tile_seq, tile_first, ctx.seq_start, ctx.seq_past, table, layer.page,
+                         num_heads, num_kv_heads, key_dim, window, rt.status, vd=value_dim, scale=scale, sink=sink, chunk=chunk)
+    else:
+        ops.attn_simt(q, layer.k, layer.v, o, ctx.tok_seq, ctx.tok_pos, table, layer.page, num_heads, num_kv_heads,
+                      key_dim, window, rt.status, vd=value_dim, scale=scale, sink=sink, chunk=chunk)
+
+
 class Attention(Part):
     """q/k/v projection (+bias), position encoding of q and k, cache write,
     causal (optionally windowed) softmax attention, output projection
@@ -245,35 +312,14 @@ class NormedAttention(Part):
     # -- which kernel a step of n token rows gets, and the index lists it needs ----------
     def kernel_for(self, n: int, page: int = PAGE) -> str:
         s = self.spec
-        if self.rt.dtype == torch.bfloat16 and page == PAGE:
-            same = s.key_dim == s.value_dim and s.scale > 0
-            if same and s.key_dim in (64, 128, 192, 256) and n <= DECODE_ROWS:
-                return "split"         # few rows: the keys are split over blocks
-            if same and ops.attn_prefill_tc05_fits(s.key_dim, page):
-                return "tc05"          # many rows: scores and weighted values in tensor memory
-            if ops.attn_flash_fits(s.key_dim, s.value_dim):
-                return "flash"         # keys and values of different sizes, any multiples of 8 up to 128
-        return "plain"
+        return scaled_kernel_for(self.rt, s.key_dim, s.value_dim, s.scale, n, page)
 
     def step_arrays_key(self):
         s = self.spec
         return ("attention_qknorm", self.rt.dtype, s.key_dim, s.value_dim, s.scale > 0)
 
     def step_arrays(self, step):
-        """Tiles of new tokens for the two tensor-core kernels of many rows: (sequence, first new token) per tile; for
-        the tensor-memory kernel the tiles that see the most keys come first (its blocks take them in order)."""
-        kind = self.kernel_for(step.n_tokens)
-        if kind == "tc05":
-            rows = ops.ATTN_TC05_TILE_ROWS
-            tiles = sorted(((i, f) for i, t in enumerate(step.news) for f in range(0, t, rows)),
-                           key=lambda sf: -(step.pasts[sf[0]] + min(sf[1] + rows, step.news[sf[0]])))
-        elif kind == "flash":
-            rows = 64
-            tiles = [(i, f) for i, t in enumerate(step.news) for f in range(0, t, rows)]
-        else:
-            return {}
-        return {f"attention.tiles{rows}.seq": np.asarray([t[0] for t in tiles], dtype=np.int32),
-                f"attention.tiles{rows}.first": np.asarray([t[1] for t in tiles], dtype=np.int32)}
+        return scaled_tiles(self.kernel_for(step.n_tokens), step)
 
     def forward(self, h, ctx, layer):
         s, rt = self.spec, self.rt
@@ -287,36 +333,8 @@ class NormedAttention(Part):
                            temp.every if temp else 0, ctx.tok_seq, ctx.tok_pos, q, layer.k, layer.v, table, layer.page,
                            s.num_heads, s.num_kv_heads, s.key_dim, s.value_dim, layer.writes, rt.status)
         o = rt.ws.get("attn_o", (n, self.o_width), rt.dtype)
-        kind = self.kernel_for(n, layer.page)
-        tile_seq = tile_first = None
-        if kind in ("tc05", "flash"):
-            rows = ops.ATTN_TC05_TILE_ROWS if kind == "tc05" else 64
-            tile_seq, tile_first = ctx.arrays.get(f"attention.tiles{rows}.seq"), ctx.arrays.get(f"attention.tiles{rows}.first")
-            if tile_seq is None:
-                kind = "plain"         # a step made without this part's lists
-        if kind == "split":
-            positions = table.shape[1] * layer.page
-            group = s.num_heads // s.num_kv_heads
-            kv_blocks = s.num_kv_heads * ((group + 15) // 16)
-            split = ops.attn_decode_split(n, kv_blocks, positions, s.key_dim, rt.sm_count)
-            n_splits = (positions + split - 1) // split
-            part_o = rt.ws.get("attn_part_o", (n, s.num_heads, n_splits, s.key_dim), torch.float32)
-            part_ml = rt.ws.get("attn_part_ml", (n, s.num_heads, n_splits, 2), torch.float32)
-            if getattr(rt, "attn_counters", None) is None:
-                rt.attn_counters = torch.zeros(ops.ATTN_DECODE_COUNTERS, dtype=torch.int32, device=rt.device)
-            ops.attn_decode(q, layer.k, layer.v, o, part_o, part_ml, rt.attn_counters, ctx.tok_seq, ctx.tok_pos, table, layer.page,
-                            s.num_heads, s.num_kv_heads, s.key_dim, s.window, split, n_splits, rt.status,
-                            seq_past=ctx.seq_past if layer.writes else None, scale=s.scale, sink=s.sink)
-        elif kind == "tc05":
-            ops.attn_prefill_tc05(q, layer.k, layer.v, o, tile_seq, tile_first, ctx.seq_start, ctx.seq_past, table, layer.page,
-                                  s.num_heads, s.num_kv_heads, s.key_dim, s.window, rt.status, scale=s.scale, sink=s.sink)
-        elif kind == "flash":
-            ops.attn_prefill(q, layer.k, layer.v, o, tile_seq, tile_first, ctx.seq_start, ctx.seq_past, table, layer.page,
-                             s.num_heads, s.num_kv_heads, s.key_dim, s.window, rt.status, vd=s.value_dim, scale=s.scale,
-                             sink=s.sink)
-        else:
-            ops.attn_simt(q, layer.k, layer.v, o, ctx.tok_seq, ctx.tok_pos, table, layer.page, s.num_heads, s.num_kv_heads,
-                          s.key_dim, s.window, rt.status, vd=s.value_dim, scale=s.scale, sink=s.sink)
+        scaled_attend(rt, self.kernel_for(n, layer.page), q, o, ctx, layer, s.num_heads, s.num_kv_heads, s.key_dim, s.value_dim,
+                      s.scale, s.sink, window=s.window)
         y = rt.ws.get("mixer_out", (n, s.hidden), torch.float32)
         linear(rt, o, self.w_o, y)
         return y
@@ -397,6 +415,18 @@ class WideNormAttention(Part):
     def state_spec(self):
         return None
 
+    # -- which kernel a step of n token rows gets, and the index lists it needs ----------
+    def kernel_for(self, n: int, page: int = PAGE) -> str:
+        s = self.spec
+        return scaled_kernel_for(self.rt, s.key_dim, s.value_dim, s.scale, n, page)
+
+    def step_arrays_key(self):
+        s = self.spec
+        return ("attention_widenorm", self.rt.dtype, s.key_dim, s.value_dim, s.scale > 0)
+
+    def step_arrays(self, step):
+        return scaled_tiles(self.kernel_for(step.n_tokens), step)
+
     def forward(self, h, ctx, layer):
         s, rt = self.spec, self.rt
         n = h.shape[0]
@@ -410,9 +440,8 @@ class WideNormAttention(Part):
                                   layer.v, table, layer.page, s.num_heads, s.num_kv_heads, s.key_dim, s.value_dim, layer.writes,
                                   rt.status)
         o = rt.ws.get("attn_o", (n, self.o_width), rt.dtype)
-        ops.attn_simt(q, layer.k, layer.v, o, ctx.tok_seq, ctx.tok_pos, table, layer.page, s.num_heads, s.num_kv_heads,
-                      s.key_dim, s.window, rt.status, vd=s.value_dim, scale=s.scale,
-                      sink=self.sink if s.learned_sink else False, chunk=s.chunk)
+        scaled_attend(rt, self.kernel_for(n, layer.page), q, o, ctx, layer, s.num_heads, s.num_kv_heads, s.key_dim, s.value_dim,
+                      s.scale, self.sink if s.learned_sink else False, window=s.window, chunk=s.chunk)
         y = rt.ws.get("mixer_out", (n, s.hidden), torch.float32)
         linear(rt, o, self.w_o, y)
         return y
