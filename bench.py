@@ -445,7 +445,7 @@ def dense_products(torch, raw, tokens=2048):
 # same width, depth and feed-forward width (the closest model this library has), both with random weights.
 def zusepel_config(width, ff, layers, vocab, window):
     heads = width // 128
-    lat = {"heads": heads, "dim": 128, "rot_dim": 64, "vdim": 128, "q_rank": 3 * width // 8, "kv_rank": width // 4,
+    lat = {"heads": heads, "dim": 128, "rot_dim": 64, "vdim": 128, "q_rank": 3 * width // 8, "kv_rank": min(512, width // 4),
            "scale": (128 + 64) ** -0.5, "mask": {"size": window},
            "rot": {"base": 10000.0, "dims": 64, "scaling": {"factor": 8.0, "fast": 32.0, "original": 4096, "slow": 1.0}}}
     pattern = [{"type": "hgrn2", "mixer": {"heads": heads, "dim": 128, "vdim": 128}},

@@ -710,12 +710,132 @@ __global__ void hc_step_kernel(float* __restrict__ streams, const float* __restr
     }
 }
 
+// The same step for S known at compile time and rows whose pieces of four channels are aligned: a thread owns pieces
+// of four channels, every copy arrives as one 16-byte load, and the loops over the copies are unrolled, so a block needs
+// few registers and several are resident.  Per element the arithmetic and its order are those of the kernel above.
+template <typename T, int S>
+__global__ void __launch_bounds__(256)
+hc_step_vec_kernel(float* __restrict__ streams, const float* __restrict__ x0, const float* __restrict__ y,
+                   const float* __restrict__ mix, const float* __restrict__ out_w, const float* __restrict__ read_w,
+                   const float* __restrict__ gamma, const int* __restrict__ rows, T* __restrict__ h,
+                   float* __restrict__ u_out, long long stream_stride, int width, float eps, int write_streams) {
+    pdl_trigger();
+    __shared__ float scratch[33];
+    float m[S * S], ow[S], rw[S];
+#pragma unroll
+    for (int i = 0; i < S * S; i++) m[i] = mix ? mix[i] : (i / S == i % S ? 1.f : 0.f);
+#pragma unroll
+    for (int s = 0; s < S; s++) {
+        ow[s] = out_w ? out_w[s] : 0.f;
+        rw[s] = read_w ? read_w[s] : 1.f;
+    }
+    pdl_wait();
+    const int i = blockIdx.x, tid = threadIdx.x;
+    const size_t r = rows ? (size_t)rows[i] : (size_t)i;
+    const float* yrow = y ? y + r * width : nullptr;
+    const float* x0row = x0 ? x0 + r * width : nullptr;
+    float* srow = streams + r * width;
+    float ss = 0.f;
+    for (int pass = 0; pass < 2; pass++) {
+        if (pass == 1 && !write_streams && !h && !u_out) break;
+        float inv = 0.f;
+        if (pass == 1) inv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)width + eps);
+        for (int d = 4 * tid; d < width; d += 4 * blockDim.x) {
+            float now[S][4];
+            {
+                float old[S][4];
+#pragma unroll
+                for (int s = 0; s < S; s++) {
+                    const float4 v = *reinterpret_cast<const float4*>(x0row ? x0row + d : srow + (size_t)s * stream_stride + d);
+                    old[s][0] = v.x, old[s][1] = v.y, old[s][2] = v.z, old[s][3] = v.w;
+                }
+                if (yrow) {
+                    const float4 y4 = *reinterpret_cast<const float4*>(yrow + d);
+                    const float yv[4] = {y4.x, y4.y, y4.z, y4.w};
+#pragma unroll
+                    for (int t = 0; t < S; t++)
+#pragma unroll
+                        for (int e = 0; e < 4; e++) {
+                            float a = 0.f;
+#pragma unroll
+                            for (int s = 0; s < S; s++) a = fmaf(m[s * S + t], old[s][e], a);
+                            now[t][e] = fmaf(ow[t], yv[e], a);
+                        }
+                } else {
+#pragma unroll
+                    for (int s = 0; s < S; s++)
+#pragma unroll
+                        for (int e = 0; e < 4; e++) now[s][e] = old[s][e];
+                }
+            }
+            float u[4];
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                float a = 0.f;
+#pragma unroll
+                for (int s = 0; s < S; s++) a = fmaf(rw[s], now[s][e], a);
+                u[e] = a;
+            }
+            if (pass == 0) {
+#pragma unroll
+                for (int e = 0; e < 4; e++) ss = fmaf(u[e], u[e], ss);
+            } else {
+                if (write_streams && (yrow || x0row)) {
+#pragma unroll
+                    for (int s = 0; s < S; s++)
+                        *reinterpret_cast<float4*>(srow + (size_t)s * stream_stride + d) =
+                            make_float4(now[s][0], now[s][1], now[s][2], now[s][3]);
+                }
+                if (u_out) *reinterpret_cast<float4*>(u_out + r * width + d) = make_float4(u[0], u[1], u[2], u[3]);
+                if (h) {
+                    const float4 g = *reinterpret_cast<const float4*>(gamma + d);
+                    Vec4<T>::store(h + (size_t)i * width + d, u[0] * inv * g.x, u[1] * inv * g.y, u[2] * inv * g.z,
+                                   u[3] * inv * g.w);
+                }
+            }
+        }
+    }
+}
+
+template <typename T, int S>
+static void hc_step_vec_launch(float* streams, const float* x0, const float* y, const float* mix, const float* out_w,
+                               const float* read_w, const float* gamma, const int* rows, T* h, float* u_out,
+                               long long stream_stride, int n_rows, int width, float eps, int write_streams,
+                               cudaStream_t stream) {
+    const int threads = width >= 2048 ? 256 : (width >= 512 ? 128 : 64);
+    esp_launch_pdl(ESP_PDL_SMALL, hc_step_vec_kernel<T, S>, dim3(n_rows), dim3(threads), 0, stream, streams, x0, y, mix, out_w,
+                   read_w, gamma, rows, h, u_out, stream_stride, width, eps, write_streams);
+}
+
+template <typename T>
+static bool hc_step_vec(float* streams, const float* x0, const float* y, const float* mix, const float* out_w,
+                        const float* read_w, const float* gamma, const int* rows, T* h, float* u_out, int S,
+                        long long stream_stride, int n_rows, int width, float eps, int write_streams, cudaStream_t stream) {
+    const size_t all = (size_t)streams | (size_t)x0 | (size_t)y | (size_t)gamma | (size_t)h | (size_t)u_out;
+    if (S > 4 || width % 4 || stream_stride % 4 || (all & 15)) return false;
+#define ESP_HC_VEC(N)                                                                                                   \
+    hc_step_vec_launch<T, N>(streams, x0, y, mix, out_w, read_w, gamma, rows, h, u_out, stream_stride, n_rows, width, \
+                             eps, write_streams, stream)
+    if (S == 1) ESP_HC_VEC(1);
+    else if (S == 2) ESP_HC_VEC(2);
+    else if (S == 3) ESP_HC_VEC(3);
+    else ESP_HC_VEC(4);
+#undef ESP_HC_VEC
+    return true;
+}
+
 ESP_API int esp_hc_step(float* streams, const float* x0, const float* y, const float* mix, const float* out_w,
                         const float* read_w, const float* gamma, const int* rows, void* h, int h_is_bf16, float* u_out,
                         int n_streams, long long stream_stride, int n_rows, int width, float eps, int write_streams,
                         cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     if (n_streams < 1 || n_streams > HC_MAX_STREAMS || width <= 0 || (h && !gamma)) return (int)cudaErrorInvalidValue;
+    // which form runs depends on the sizes and the buffers' alignment alone, never on the rows of a step
+    if (h_is_bf16 ? hc_step_vec<bf16>(streams, x0, y, mix, out_w, read_w, gamma, rows, (bf16*)h, u_out, n_streams, stream_stride,
+                                      n_rows, width, eps, write_streams, stream)
+                  : hc_step_vec<float>(streams, x0, y, mix, out_w, read_w, gamma, rows, (float*)h, u_out, n_streams,
+                                       stream_stride, n_rows, width, eps, write_streams, stream))
+        return esp_launch_status();
     const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
     if (h_is_bf16)
         esp_launch_pdl(ESP_PDL_SMALL, hc_step_kernel<bf16>, dim3(n_rows), dim3(threads), 0, stream, streams, x0, y, mix, out_w,

@@ -445,12 +445,14 @@ def test_gated_unit_with_clamped_branches(limit, dtype):
     assert (act.double().cpu() - want).abs().max() < (1e-5 if dtype == torch.float32 else 2e-2) * float(want.abs().max())
 
 
-@pytest.mark.parametrize("S", [1, 2, 3, 5])
-def test_write_to_all_copies_of_the_residual_stream_then_read(S):
+@pytest.mark.parametrize("D", [52, 50, 1028])
+@pytest.mark.parametrize("S", [1, 2, 3, 4, 5])
+def test_write_to_all_copies_of_the_residual_stream_then_read(S, D):
     """The mixing matrix is far from symmetric, so [from, to] and [to, from] differ; all copies are written from the old
-    ones at once."""
+    ones at once.  Widths of whole pieces of four channels with few copies take the kernel of 16-byte accesses, the
+    others the kernel of single channels."""
     g = torch.Generator().manual_seed(S)
-    n, D, eps = 7, 52, 1e-5
+    n, eps = 7, 1e-5
     streams = torch.randn(S, n, D, generator=g)
     y = torch.randn(n, D, generator=g)
     mix = torch.triu(torch.randn(S, S, generator=g)) + torch.eye(S)
