@@ -229,6 +229,70 @@ __global__ void causal_conv_kernel(const float* __restrict__ x, long long ldx, c
     }
 }
 
+// The same convolution for a reach known at compile time and rows whose pieces of four channels are aligned: a block
+// takes CONV_TILE_ROWS rows and a thread four channels of them, with the last TAPS inputs of its channels in registers.
+// Stepping to the next row shifts that window and loads one row; a row that opens a sequence's run (or the tile) fills
+// it from the earlier rows or the sequence's state.  Per element the sum runs over the taps in the order of the kernel
+// above.
+constexpr int CONV_TILE_ROWS = 16;
+template <int TAPS>
+__global__ void __launch_bounds__(64)
+causal_conv_tile_kernel(const float* __restrict__ x, long long ldx, const float* __restrict__ w,
+                        const float* __restrict__ conv_state, long long state_stride,
+                        const int* __restrict__ tok_seq, const int* __restrict__ seq_start,
+                        const int* __restrict__ seq_slot, float* __restrict__ y, int n_rows, int C, int act) {
+    pdl_trigger();
+    const int c = 4 * (blockIdx.y * blockDim.x + threadIdx.x);
+    if (c >= C) return;
+    float wt[4][TAPS];
+#pragma unroll
+    for (int e = 0; e < 4; e++)
+#pragma unroll
+        for (int j = 0; j < TAPS; j++) wt[e][j] = w[(size_t)(c + e) * TAPS + j];
+    pdl_wait();
+    const int first = blockIdx.x * CONV_TILE_ROWS;
+    const int last = min(first + CONV_TILE_ROWS, n_rows);
+    float4 win[TAPS];                                   // win[j]: the input `TAPS - 1 - j` rows back
+    for (int n = first; n < last; n++) {
+        const int seq = tok_seq[n];
+        const int in_run = n - seq_start[seq];
+        if (n == first || in_run == 0) {
+            const float* st = conv_state + (size_t)seq_slot[seq] * state_stride;
+#pragma unroll
+            for (int j = 0; j < TAPS - 1; j++) {
+                const int back = TAPS - 1 - j;
+                win[j] = *reinterpret_cast<const float4*>(in_run - back >= 0 ? x + (size_t)(n - back) * ldx + c
+                                                                              : st + (size_t)(TAPS - 1 + in_run - back) * C + c);
+            }
+        }
+        win[TAPS - 1] = *reinterpret_cast<const float4*>(x + (size_t)n * ldx + c);
+        float u[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int j = 0; j < TAPS; j++) {
+            u[0] = fmaf(wt[0][j], win[j].x, u[0]);
+            u[1] = fmaf(wt[1][j], win[j].y, u[1]);
+            u[2] = fmaf(wt[2][j], win[j].z, u[2]);
+            u[3] = fmaf(wt[3][j], win[j].w, u[3]);
+        }
+        if (act == 1) {
+#pragma unroll
+            for (int e = 0; e < 4; e++) u[e] = u[e] * sigmoid_f(u[e]);
+        }
+        *reinterpret_cast<float4*>(y + (size_t)n * C + c) = make_float4(u[0], u[1], u[2], u[3]);
+#pragma unroll
+        for (int j = 0; j < TAPS - 1; j++) win[j] = win[j + 1];
+    }
+}
+
+template <int TAPS>
+static void causal_conv_tile_launch(const float* x, long long ldx, const float* w, const float* conv_state,
+                                    long long state_stride, const int* tok_seq, const int* seq_start, const int* seq_slot,
+                                    float* y, int n_rows, int C, int act, cudaStream_t stream) {
+    esp_launch_pdl(ESP_PDL_SMALL, causal_conv_tile_kernel<TAPS>,
+                   dim3((n_rows + CONV_TILE_ROWS - 1) / CONV_TILE_ROWS, (C / 4 + 63) / 64), dim3(64), 0, stream, x, ldx, w,
+                   conv_state, state_stride, tok_seq, seq_start, seq_slot, y, n_rows, C, act);
+}
+
 // state[slot] <- the last taps - 1 inputs of the sequence after this step (a thread owns a channel: it reads what it
 // needs of the old state before it writes).
 constexpr int CONV_MAX_TAPS = 16;
@@ -305,8 +369,19 @@ ESP_API int esp_causal_conv(const float* x, long long ldx, const float* w, float
                             int C, int taps, int act, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     if (taps < 1 || taps > CONV_MAX_TAPS || C <= 0) return (int)cudaErrorInvalidValue;
-    esp_launch_pdl(ESP_PDL_SMALL, causal_conv_kernel, dim3(n_rows), dim3(C >= 1024 ? 256 : 128), 0, stream, x, ldx, w,
-                   (const float*)conv_state, state_stride, tok_seq, seq_start, seq_slot, y, C, taps, act);
+    // which form runs depends on the sizes and the buffers' alignment alone, never on the rows of a step
+    const bool tiled = taps >= 2 && taps <= 4 && C % 4 == 0 && ldx % 4 == 0 && state_stride % 4 == 0 &&
+                       (((size_t)x | (size_t)conv_state | (size_t)y) & 15) == 0;
+#define ESP_CONV_TILE(N)                                                                                               \
+    causal_conv_tile_launch<N>(x, ldx, w, (const float*)conv_state, state_stride, tok_seq, seq_start, seq_slot, y, n_rows, C, \
+                               act, stream)
+    if (tiled && taps == 2) ESP_CONV_TILE(2);
+    else if (tiled && taps == 3) ESP_CONV_TILE(3);
+    else if (tiled) ESP_CONV_TILE(4);
+    else
+        esp_launch_pdl(ESP_PDL_SMALL, causal_conv_kernel, dim3(n_rows), dim3(C >= 1024 ? 256 : 128), 0, stream, x, ldx, w,
+                       (const float*)conv_state, state_stride, tok_seq, seq_start, seq_slot, y, C, taps, act);
+#undef ESP_CONV_TILE
     if (taps > 1)
         esp_launch_pdl(ESP_PDL_SMALL, causal_conv_keep_kernel, dim3(n_seqs, (C + 127) / 128), dim3(128), 0, stream, x, ldx,
                        conv_state, state_stride, seq_start, seq_slot, C, taps);

@@ -221,20 +221,22 @@ def test_norm_over_the_whole_projection_then_rotation_of_the_first_channels(H, G
 
 
 # ------------------------------------------------------------------------------------------ short convolution
-@pytest.mark.parametrize("taps", [1, 2, 4, 7])
-def test_convolution_cut_in_the_middle_of_its_reach(taps):
+@pytest.mark.parametrize("C,lead,pad", [(37, 11, 9), (40, 12, 12)])
+@pytest.mark.parametrize("taps", [1, 2, 3, 4, 7])
+def test_convolution_cut_in_the_middle_of_its_reach(taps, C, lead, pad):
     """Three sequences in slots 5, 0, 2, cut into steps of 1, 2, 3 and more rows so that a cut falls inside the reach of
-    the taps again and again; the kept inputs move from step to step.  One sequence is shorter than the taps."""
-    C = 37
+    the taps again and again; the kept inputs move from step to step.  One sequence is shorter than the taps.  With 40
+    channels and aligned rows a short reach takes the kernel that walks tiles of rows (a run may begin inside a tile),
+    otherwise the kernel of single rows."""
     g = torch.Generator().manual_seed(taps)
     w = torch.randn(C, taps, generator=g)
-    lengths, slots = [29, taps - 1 if taps > 1 else 1, 12], [5, 0, 2]
+    lengths, slots = [45, taps - 1 if taps > 1 else 1, 12], [5, 0, 2]
     xs = [torch.randn(L, C, generator=g) for L in lengths]
     want = [plain.silu(plain.causal_conv(x.double(), w.double())) for x in xs]
-    state = torch.full((6, 11 + (taps - 1) * C), 7.0, device=DEV)          # other state ahead of the kept inputs
-    conv_state = state[:, 11:] if taps > 1 else None
+    state = torch.full((6, lead + (taps - 1) * C), 7.0, device=DEV)        # other state ahead of the kept inputs
+    conv_state = state[:, lead:] if taps > 1 else None
     if taps > 1:
-        state[:, 11:] = 0.0                                                # what opening a slot does
+        state[:, lead:] = 0.0                                                # what opening a slot does
     got = [torch.zeros(L, C) for L in lengths]
     at = [0, 0, 0]
     cuts = [1, 2, 3, 1, 5, 2, 64]
@@ -243,7 +245,7 @@ def test_convolution_cut_in_the_middle_of_its_reach(taps):
         live = [i for i in range(3) if at[i] < lengths[i]]
         take = [min(cuts[(step + i) % len(cuts)], lengths[i] - at[i]) for i in live]
         x = torch.cat([xs[i][at[i]:at[i] + t] for i, t in zip(live, take)])
-        wide = torch.zeros(x.shape[0], C + 9)                              # rows that are parts of wider rows
+        wide = torch.zeros(x.shape[0], C + pad)                              # rows that are parts of wider rows
         wide[:, 4:4 + C] = x
         wide = dev(wide)
         y = torch.zeros(x.shape[0], C, device=DEV)
@@ -258,9 +260,9 @@ def test_convolution_cut_in_the_middle_of_its_reach(taps):
         step += 1
     for i in range(3):
         assert (got[i].double() - want[i]).abs().max() < 1e-5, i
-    assert float(state[:, :11].min()) == 7.0                               # the kernel keeps to its part of the state rows
+    assert float(state[:, :lead].min()) == 7.0                               # the kernel keeps to its part of the state rows
     if taps > 1:
-        kept = state[5, 11:].view(taps - 1, C).cpu()
+        kept = state[5, lead:].view(taps - 1, C).cpu()
         assert torch.equal(kept, xs[0][-(taps - 1):])
 
 
@@ -429,12 +431,24 @@ def test_norm_of_every_head_with_one_weight_for_all_heads_and_a_gate(H, V, sigmo
 
 
 # -------------------------------------------------------------------------------- feed-forward, residual streams
+@pytest.mark.parametrize("n_parts", [1, 2, 4])
+@pytest.mark.parametrize("count", [3 * 52, 3 * 53])
+def test_branches_side_by_side_are_added_with_a_weight_each(n_parts, count):
+    g = torch.Generator().manual_seed(count + n_parts)
+    parts = [torch.randn(3, count // 3, generator=g) for _ in range(n_parts)]
+    scales = [0.5, -1.25, 2.0, 0.125][:n_parts]
+    out = torch.zeros(3, count // 3, device=DEV)
+    ops.weighted_sum(out, [dev(p) for p in parts], scales)
+    want = sum(s * p.double() for s, p in zip(scales, parts))
+    assert (out.double().cpu() - want).abs().max() < 1e-5
+
+
+@pytest.mark.parametrize("I", [50, 52])
 @pytest.mark.parametrize("limit", [0.5, 7.0])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_gated_unit_with_clamped_branches(limit, dtype):
+def test_gated_unit_with_clamped_branches(limit, dtype, I):
     """The gate is cut from above only (a very negative gate stays and gives nearly nothing), the linear branch on both
     sides, before one is added to it."""
-    I = 50
     gu = torch.randn(13, 2 * I, generator=torch.Generator().manual_seed(5)) * 4
     gu[0, :4] = torch.tensor([-30.0, 30.0, limit, -limit])
     gu[0, I:I + 4] = torch.tensor([30.0, -30.0, -limit - 0.1, limit + 0.1])
