@@ -234,7 +234,7 @@ __global__ void causal_conv_kernel(const float* __restrict__ x, long long ldx, c
 // Stepping to the next row shifts that window and loads one row; a row that opens a sequence's run (or the tile) fills
 // it from the earlier rows or the sequence's state.  Per element the sum runs over the taps in the order of the kernel
 // above.
-constexpr int CONV_TILE_ROWS = 16;
+constexpr int CONV_TILE_ROWS = 8;
 template <int TAPS>
 __global__ void __launch_bounds__(64)
 causal_conv_tile_kernel(const float* __restrict__ x, long long ldx, const float* __restrict__ w,
@@ -252,8 +252,16 @@ causal_conv_tile_kernel(const float* __restrict__ x, long long ldx, const float*
     pdl_wait();
     const int first = blockIdx.x * CONV_TILE_ROWS;
     const int last = min(first + CONV_TILE_ROWS, n_rows);
+    float4 own[CONV_TILE_ROWS];                         // the tile's own inputs, all loads in flight together
+#pragma unroll
+    for (int i = 0; i < CONV_TILE_ROWS; i++)
+        own[i] = first + i < last ? *reinterpret_cast<const float4*>(x + (size_t)(first + i) * ldx + c)
+                                  : make_float4(0.f, 0.f, 0.f, 0.f);
     float4 win[TAPS];                                   // win[j]: the input `TAPS - 1 - j` rows back
-    for (int n = first; n < last; n++) {
+#pragma unroll
+    for (int i = 0; i < CONV_TILE_ROWS; i++) {
+        const int n = first + i;
+        if (n >= last) break;
         const int seq = tok_seq[n];
         const int in_run = n - seq_start[seq];
         if (n == first || in_run == 0) {
@@ -265,7 +273,7 @@ causal_conv_tile_kernel(const float* __restrict__ x, long long ldx, const float*
                                                                               : st + (size_t)(TAPS - 1 + in_run - back) * C + c);
             }
         }
-        win[TAPS - 1] = *reinterpret_cast<const float4*>(x + (size_t)n * ldx + c);
+        win[TAPS - 1] = own[i];
         float u[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
         for (int j = 0; j < TAPS; j++) {

@@ -299,6 +299,11 @@ __global__ void widenorm_rope_kvwrite_kernel(const float* __restrict__ qkv, cons
     const float inv_k = k_w ? 1.0f / sqrtf(block_sum(ssk, scratch) / (float)kw + eps) : 1.0f;
     const int half = rot / 2;
     const float p = (float)pos;
+    // the row's angles are the same for every head: their cosines and sines are made once (dynamic shared memory:
+    // rot floats), from the same expression a head of its own would evaluate
+    extern __shared__ float rot_cs[];
+    for (int c = tid; c < half; c += blockDim.x) sincosf(p * inv_freq[c], &rot_cs[half + c], &rot_cs[c]);
+    __syncthreads();
     for (int e = tid; e < qw + kw; e += blockDim.x) {
         const bool is_q = e < qw;
         const int local = is_q ? e : e - qw;
@@ -315,8 +320,7 @@ __global__ void widenorm_rope_kvwrite_kernel(const float* __restrict__ qkv, cons
         if (c < half) {
             float b = src[e + half];
             if (w) b = b * inv * w[local + half];
-            float sn, cs;
-            sincosf(p * inv_freq[c], &sn, &cs);
+            const float cs = rot_cs[c], sn = rot_cs[half + c];
             dst[c] = from_f32<T>(a * cs - b * sn);
             dst[c + half] = from_f32<T>(b * cs + a * sn);
         } else {
@@ -341,11 +345,11 @@ ESP_API int esp_widenorm_rope_kvwrite(const float* qkv, const float* q_w, const 
         return (int)cudaErrorInvalidValue;
     const int threads = (nh + nkv) * hd >= 2048 ? 256 : 128;
     if (is_bf16)
-        esp_launch_pdl(ESP_PDL_SMALL, widenorm_rope_kvwrite_kernel<bf16>, dim3(n_tokens), dim3(threads), 0, stream, qkv, q_w, k_w,
+        esp_launch_pdl(ESP_PDL_SMALL, widenorm_rope_kvwrite_kernel<bf16>, dim3(n_tokens), dim3(threads), rot * sizeof(float), stream, qkv, q_w, k_w,
                        eps, inv_freq, rot, v_scale, tok_seq, tok_pos, (bf16*)q_out, (bf16*)k_cache, (bf16*)v_cache, block_table,
                        table_stride, n_pages, page, nh, nkv, hd, vd, write_kv, status);
     else
-        esp_launch_pdl(ESP_PDL_SMALL, widenorm_rope_kvwrite_kernel<float>, dim3(n_tokens), dim3(threads), 0, stream, qkv, q_w, k_w,
+        esp_launch_pdl(ESP_PDL_SMALL, widenorm_rope_kvwrite_kernel<float>, dim3(n_tokens), dim3(threads), rot * sizeof(float), stream, qkv, q_w, k_w,
                        eps, inv_freq, rot, v_scale, tok_seq, tok_pos, (float*)q_out, (float*)k_cache, (float*)v_cache,
                        block_table, table_stride, n_pages, page, nh, nkv, hd, vd, write_kv, status);
     return esp_launch_status();
