@@ -335,6 +335,102 @@ __global__ void widenorm_rope_kvwrite_kernel(const float* __restrict__ qkv, cons
     }
 }
 
+// The same for head sizes, value sizes and half a rotation of whole pieces of four channels, and aligned buffers.  The
+// row's query and key part is read once, in 16-byte loads, into shared memory (the sums of squares are taken on the
+// way, both reduced in one exchange).  A thread then makes four
+// neighbouring channels and, where they are rotated, their four partners, and stores each as one piece.  Per element the
+// arithmetic is that of the kernel above; only the order in which the squares are added differs.
+// Dynamic shared memory: (nh * hd + nkv * hd + rot) floats.
+template <typename T>
+__global__ void __launch_bounds__(256)
+widenorm_rope_kvwrite_vec_kernel(const float* __restrict__ qkv, const float* __restrict__ q_w,
+                                 const float* __restrict__ k_w, float eps, const float* __restrict__ inv_freq, int rot,
+                                 float v_scale, const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
+                                 T* __restrict__ q_out, T* __restrict__ k_cache, T* __restrict__ v_cache,
+                                 const int* __restrict__ block_table, int table_stride, int n_pages, int page, int nh,
+                                 int nkv, int hd, int vd, int write_kv, int* __restrict__ status) {
+    pdl_trigger();
+    extern __shared__ __align__(16) float row_smem[];
+    __shared__ float part[2][8];
+    const int n = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarp = blockDim.x >> 5;
+    const int qw = nh * hd, kw = nkv * hd, vw = nkv * vd, half = rot / 2;
+    float* row = row_smem;
+    float* rot_cs = row_smem + qw + kw;
+    pdl_wait();
+    const int pos = tok_pos[n], seq = tok_seq[n];
+    const float p = (float)pos;
+    for (int c = tid; c < half; c += blockDim.x) sincosf(p * inv_freq[c], &rot_cs[half + c], &rot_cs[c]);
+    int page_id = -1;
+    if (write_kv) {
+        page_id = block_table[(size_t)seq * table_stride + pos / page];
+        if (page_id < 0 || page_id >= n_pages) {
+            if (tid == 0) atomicOr(status, ESP_STATUS_BAD_INDEX);
+            page_id = -1;
+        }
+    }
+    const int in_page = pos % page;
+    const float* src = qkv + (size_t)n * (qw + kw + vw);
+    float ssq = 0.f, ssk = 0.f;
+    for (int e = 4 * tid; e < qw + kw; e += 4 * blockDim.x) {
+        const float4 v = *reinterpret_cast<const float4*>(src + e);
+        *reinterpret_cast<float4*>(row + e) = v;
+        const float s4 = fmaf(v.w, v.w, fmaf(v.z, v.z, fmaf(v.y, v.y, v.x * v.x)));
+        if (e < qw) ssq += s4; else ssk += s4;
+    }
+    ssq = warp_sum(ssq), ssk = warp_sum(ssk);
+    if (lane == 0) part[0][warp] = ssq, part[1][warp] = ssk;
+    __syncthreads();
+    float tq = 0.f, tk = 0.f;
+    for (int i = 0; i < nwarp; i++) tq += part[0][i], tk += part[1][i];
+    const float inv_q = q_w ? 1.0f / sqrtf(tq / (float)qw + eps) : 1.0f;
+    const float inv_k = k_w ? 1.0f / sqrtf(tk / (float)kw + eps) : 1.0f;
+    for (int e = 4 * tid; e < qw + kw; e += 4 * blockDim.x) {
+        const bool is_q = e < qw;
+        const int local = is_q ? e : e - qw;
+        const int head = local / hd, c = local - head * hd;
+        if (c >= half && c < rot) continue;               // written with the first halves of their pairs
+        const float* w = is_q ? q_w : k_w;
+        const float inv = is_q ? inv_q : inv_k;
+        T* dst;
+        if (is_q) dst = q_out + ((size_t)n * nh + head) * hd;
+        else if (page_id >= 0) dst = k_cache + (((size_t)page_id * nkv + head) * page + in_page) * hd;
+        else continue;
+        const float4 a4 = *reinterpret_cast<const float4*>(row + e);
+        float a[4] = {a4.x, a4.y, a4.z, a4.w};
+        if (w) {
+            const float4 w4 = *reinterpret_cast<const float4*>(w + local);
+            a[0] = a[0] * inv * w4.x, a[1] = a[1] * inv * w4.y, a[2] = a[2] * inv * w4.z, a[3] = a[3] * inv * w4.w;
+        }
+        if (c < half) {
+            const float4 b4 = *reinterpret_cast<const float4*>(row + e + half);
+            float b[4] = {b4.x, b4.y, b4.z, b4.w};
+            if (w) {
+                const float4 w4 = *reinterpret_cast<const float4*>(w + local + half);
+                b[0] = b[0] * inv * w4.x, b[1] = b[1] * inv * w4.y, b[2] = b[2] * inv * w4.z, b[3] = b[3] * inv * w4.w;
+            }
+            float lo[4], hi[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const float cs = rot_cs[c + i], sn = rot_cs[half + c + i];
+                lo[i] = a[i] * cs - b[i] * sn;
+                hi[i] = b[i] * cs + a[i] * sn;
+            }
+            Vec4<T>::store(dst + c, lo[0], lo[1], lo[2], lo[3]);
+            Vec4<T>::store(dst + c + half, hi[0], hi[1], hi[2], hi[3]);
+        } else {
+            Vec4<T>::store(dst + c, a[0], a[1], a[2], a[3]);
+        }
+    }
+    if (page_id >= 0) {
+        for (int e = 4 * tid; e < vw; e += 4 * blockDim.x) {
+            const int head = e / vd, c = e - head * vd;
+            const float4 v = *reinterpret_cast<const float4*>(src + qw + kw + e);
+            Vec4<T>::store(v_cache + (((size_t)page_id * nkv + head) * page + in_page) * vd + c, v.x * v_scale, v.y * v_scale,
+                           v.z * v_scale, v.w * v_scale);
+        }
+    }
+}
+
 ESP_API int esp_widenorm_rope_kvwrite(const float* qkv, const float* q_w, const float* k_w, float eps, const float* inv_freq,
                                       int rot, float v_scale, const int* tok_seq, const int* tok_pos, void* q_out,
                                       void* k_cache, void* v_cache, int is_bf16, const int* block_table, int table_stride,
@@ -344,6 +440,20 @@ ESP_API int esp_widenorm_rope_kvwrite(const float* qkv, const float* q_w, const 
     if (hd <= 0 || vd <= 0 || nkv <= 0 || nh <= 0 || page <= 0 || rot < 0 || rot > hd || rot % 2 != 0 || (rot > 0 && !inv_freq))
         return (int)cudaErrorInvalidValue;
     const int threads = (nh + nkv) * hd >= 2048 ? 256 : 128;
+    // which form runs depends on the sizes and the buffers' alignment alone, never on the rows of a step
+    const size_t row_bytes = (size_t)((nh + nkv) * hd + rot) * sizeof(float);
+    const size_t ptrs = (size_t)qkv | (size_t)q_w | (size_t)k_w | (size_t)q_out | (size_t)k_cache | (size_t)v_cache;
+    if (hd % 4 == 0 && vd % 4 == 0 && rot % 8 == 0 && (ptrs & 15) == 0 && row_bytes <= 40 * 1024) {
+        if (is_bf16)
+            esp_launch_pdl(ESP_PDL_SMALL, widenorm_rope_kvwrite_vec_kernel<bf16>, dim3(n_tokens), dim3(threads), row_bytes, stream,
+                           qkv, q_w, k_w, eps, inv_freq, rot, v_scale, tok_seq, tok_pos, (bf16*)q_out, (bf16*)k_cache,
+                           (bf16*)v_cache, block_table, table_stride, n_pages, page, nh, nkv, hd, vd, write_kv, status);
+        else
+            esp_launch_pdl(ESP_PDL_SMALL, widenorm_rope_kvwrite_vec_kernel<float>, dim3(n_tokens), dim3(threads), row_bytes, stream,
+                           qkv, q_w, k_w, eps, inv_freq, rot, v_scale, tok_seq, tok_pos, (float*)q_out, (float*)k_cache,
+                           (float*)v_cache, block_table, table_stride, n_pages, page, nh, nkv, hd, vd, write_kv, status);
+        return esp_launch_status();
+    }
     if (is_bf16)
         esp_launch_pdl(ESP_PDL_SMALL, widenorm_rope_kvwrite_kernel<bf16>, dim3(n_tokens), dim3(threads), rot * sizeof(float), stream, qkv, q_w, k_w,
                        eps, inv_freq, rot, v_scale, tok_seq, tok_pos, (bf16*)q_out, (bf16*)k_cache, (bf16*)v_cache, block_table,
