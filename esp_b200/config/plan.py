@@ -15,7 +15,7 @@ from typing import Any, Optional
 
 @dataclass(frozen=True)
 class NormSpec:
-    kind: str            # registry key, e.g. "rmsnorm"
+    kind: str            # registry key, e.g. "rmsnorm"; "rmsnorm_offset": the stored weight lies around zero, the scale is 1 + w
     width: int
     eps: float
     weight: str          # tensor name of the scale vector
@@ -85,18 +85,39 @@ class DenseFfnSpec:
 
 
 @dataclass(frozen=True)
+class Relu2FfnSpec:
+    """down(relu(up h)^2), no biases."""
+    hidden: int
+    intermediate: int
+    prefix: str
+    kind: str = "relu2"
+    up: str = "up"
+    down: str = "down"
+
+
+@dataclass(frozen=True)
 class MoeFfnSpec:
     """Softmax router, top-k routed SwiGLU experts, one shared SwiGLU expert
-    scaled by a sigmoid gate."""
+    scaled by a sigmoid gate (``shared_intermediate`` None: no shared expert).
+
+    ``identity_experts``: the router has that many outputs more than there are experts with weights; an expert
+    chosen among them returns its input (times its routing weight).  ``correction``: the name of a tensor with one
+    number per router output that is added to the score for the choice only; the weights stay the scores.
+    ``groups`` / ``keep_groups``: the router's outputs form that many equal groups of neighbours, a group's score is
+    its largest corrected score, and only experts of the best ``keep_groups`` groups can be chosen."""
     hidden: int
     num_experts: int
     top_k: int
     norm_topk: bool
     expert_intermediate: int
-    shared_intermediate: int
+    shared_intermediate: Optional[int]
     prefix: str
     kind: str = "moe_swiglu_shared"
     names: MoeNames = MoeNames()
+    identity_experts: int = 0
+    correction: Optional[str] = None
+    groups: int = 0
+    keep_groups: int = 0
 
 
 @dataclass(frozen=True)
@@ -125,13 +146,17 @@ class LatentAttentionNames:
     k_up: str = "uk"
     v_up: str = "uv"
     o: str = "o"
+    q: str = "q"                     # full-rank queries (q_rank None)
+    head_gate: str = "g"
 
 
 @dataclass(frozen=True)
 class LatentAttentionSpec:
     """Softmax attention whose keys and values are up-projections of one cached latent per position; the keys have,
     besides, one rotated part that is the same for every head.  Per head: ``nope_dim`` unrotated and ``rot_dim`` rotated query/key
-    channels, ``value_dim`` value channels."""
+    channels, ``value_dim`` value channels.  ``q_rank`` None: the queries are one full-rank projection of the layer's
+    input.  ``rot_dim`` 0 with ``position`` None: no rotated part and no positions at all.  ``head_gate``: every head's
+    output is multiplied by the sigmoid of one number per token and head, a projection of the layer's input."""
     hidden: int
     num_heads: int
     nope_dim: int
@@ -143,11 +168,12 @@ class LatentAttentionSpec:
     window: Optional[int]            # None: every earlier key; W: the query and W-1 predecessors
     keep_window: Optional[int]       # how far back the cache has to reach for every layer that reads it
     eps: float                       # of the two latent norms
-    position: ScaledRopeSpec
+    position: Optional[ScaledRopeSpec]
     own_kv: bool                     # False: the layer has no down-projection and reads another layer's cache
     prefix: str
     kind: str = "latent_attention"
     names: LatentAttentionNames = LatentAttentionNames()
+    head_gate: bool = False
 
 
 @dataclass(frozen=True)
@@ -540,12 +566,89 @@ class HyperConnectionBlockSpec:
 
 
 @dataclass(frozen=True)
+class NeighbourRopeSpec:
+    """Rotary encoding over neighbouring channels: of the first ``rotary_dim`` channels of a head, channel 2i is
+    rotated with channel 2i + 1 by the angle position * theta^(-2i / rotary_dim)."""
+    rotary_dim: int
+    theta: float
+    factor: Optional[float] = None   # no interpolation in this form
+    kind: str = "rope_neighbour_pairs"
+
+
+@dataclass(frozen=True)
+class UnitNormAttentionNames:
+    q: str = "q"
+    k: str = "k"
+    v: str = "v"
+    o: str = "o"
+    bias: str = ".b"
+    sink: str = "sink"
+    value_blend: str = "vmix"
+
+
+@dataclass(frozen=True)
+class UnitNormAttentionSpec:
+    """Causal softmax attention over cached keys and values with grouped query heads: projections with optional
+    biases; rotation of neighbouring channel pairs of the first channels of every head (``position``); then, with
+    ``unit_heads``, queries and keys divided by their root mean square per head (no weight); scores times ``scale``
+    as given; a window; ``learned_sink``: one more term exp(sink_h) per head in the softmax's denominator, unscaled,
+    without a value.  ``value_blend``: "first" marks the layer whose values (of the step's tokens) later layers
+    blend with; "blend": v <- (1 - lambda) v + lambda v_first with lambda a learned number, and the blended values
+    are what the cache holds; None: neither.  A "first" layer still names lambda's tensor (a checkpoint holds it)."""
+    hidden: int
+    num_heads: int
+    num_kv_heads: int
+    key_dim: int
+    value_dim: int
+    scale: float
+    eps: float
+    qkv_bias: bool
+    unit_heads: bool
+    learned_sink: bool
+    window: Optional[int]
+    position: Optional[NeighbourRopeSpec]
+    value_blend: Optional[str]
+    prefix: str
+    kind: str = "attention_unitnorm"
+    names: UnitNormAttentionNames = UnitNormAttentionNames()
+
+
+@dataclass(frozen=True)
+class SelectiveScanNames:
+    in_proj: str = "in"
+    conv: str = "conv"
+    conv_bias: str = "conv.b"
+    x_proj: str = "x"
+    dt_proj: str = "dt"
+    dt_bias: str = "dt.b"
+    a_log: str = "A_log"
+    skip: str = "D"
+    o: str = "o"
+
+
+@dataclass(frozen=True)
+class SelectiveScanSpec:
+    """W_in h = [x | z] of ``inner`` channels each; x passes a causal convolution of ``taps`` per channel with a bias,
+    then SiLU; W_x x = [dt_low (dt_rank) | B (state) | C (state)]; dt = softplus(W_dt dt_low + bias) per channel;
+    per channel c and state entry n: S <- exp(-dt exp(a_log[c, n])) S + dt x_c B_n; y_c = S[c] . C + skip_c x_c; the
+    result times silu(z), then W_o."""
+    hidden: int
+    inner: int
+    state: int
+    dt_rank: int
+    taps: int
+    prefix: str
+    kind: str = "selective_scan"
+    names: SelectiveScanNames = SelectiveScanNames()
+
+
+@dataclass(frozen=True)
 class BlockSpec:
-    """One layer: which parts it has and how they are arranged."""
+    """One layer: which parts it has and how they are arranged.  ``ffn`` (and ``ffn_norm``) None: a mixer only."""
     mixer: Any                       # any spec object with a ``kind``
     ffn: Any
     mixer_norm: NormSpec
-    ffn_norm: NormSpec
+    ffn_norm: Optional[NormSpec]
     kind: str = "prenorm_residual"   # x += mixer(norm(x)); x += ffn(norm(x))
 
 

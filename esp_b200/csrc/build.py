@@ -32,7 +32,7 @@ LIBRARIES = {
     "core": ["elementwise.cu", "gemm_simt.cu", "rope_kv.cu", "attn_simt.cu", "moe_route.cu", "sampling.cu"],
     # layers with a recurrent state and attention through a cached latent (every dtype); a library of its own, so
     # that a model without such layers does not compile it
-    "mixers": ["recurrent.cu", "latent.cu", "delta.cu"],
+    "mixers": ["recurrent.cu", "latent.cu", "delta.cu", "selective.cu"],
     # bfloat16 only: loaded when a model runs in bfloat16
     "bf16": ["gemm_skinny.cu", "attn_decode.cu", "attn_prefill.cu", "attn_latent_mma.cu"],
     # TMA + tcgen05/TMEM products for steps with many rows (bfloat16 prefill)

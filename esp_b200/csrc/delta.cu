@@ -207,8 +207,10 @@ __global__ void channel_decay_prepare_kernel(float* __restrict__ z, const float*
 
 // y[n, c] = act(sum_j w[c, j] x[n - (taps - 1) + j, c]) over the rows of a sequence, the last column of w being the
 // token's own; inputs ahead of a run's first token come from the sequence's state (state[slot]: [taps - 1, C],
-// oldest first; zeros in a fresh slot).  act: 0 none, 1 SiLU.  x: float rows with stride ldx; y: float [rows, C].
+// oldest first; zeros in a fresh slot).  bias (may be null): a number per channel added to the sum before the
+// activation.  act: 0 none, 1 SiLU.  x: float rows with stride ldx; y: float [rows, C].
 __global__ void causal_conv_kernel(const float* __restrict__ x, long long ldx, const float* __restrict__ w,
+                                   const float* __restrict__ bias,
                                    const float* __restrict__ conv_state, long long state_stride,
                                    const int* __restrict__ tok_seq, const int* __restrict__ seq_start,
                                    const int* __restrict__ seq_slot, float* __restrict__ y, int C, int taps, int act) {
@@ -225,6 +227,7 @@ __global__ void causal_conv_kernel(const float* __restrict__ x, long long ldx, c
             const float xin = in_run - back >= 0 ? x[(size_t)(n - back) * ldx + c] : st[(size_t)(taps - 1 + in_run - back) * C + c];
             u = fmaf(w[(size_t)c * taps + j], xin, u);
         }
+        if (bias) u += bias[c];
         y[(size_t)n * C + c] = act == 1 ? u * sigmoid_f(u) : u;
     }
 }
@@ -238,6 +241,7 @@ constexpr int CONV_TILE_ROWS = 8;
 template <int TAPS>
 __global__ void __launch_bounds__(64)
 causal_conv_tile_kernel(const float* __restrict__ x, long long ldx, const float* __restrict__ w,
+                        const float* __restrict__ bias,
                         const float* __restrict__ conv_state, long long state_stride,
                         const int* __restrict__ tok_seq, const int* __restrict__ seq_start,
                         const int* __restrict__ seq_slot, float* __restrict__ y, int n_rows, int C, int act) {
@@ -249,6 +253,11 @@ causal_conv_tile_kernel(const float* __restrict__ x, long long ldx, const float*
     for (int e = 0; e < 4; e++)
 #pragma unroll
         for (int j = 0; j < TAPS; j++) wt[e][j] = w[(size_t)(c + e) * TAPS + j];
+    float bs[4] = {0.f, 0.f, 0.f, 0.f};
+    if (bias) {
+#pragma unroll
+        for (int e = 0; e < 4; e++) bs[e] = bias[c + e];
+    }
     pdl_wait();
     const int first = blockIdx.x * CONV_TILE_ROWS;
     const int last = min(first + CONV_TILE_ROWS, n_rows);
@@ -282,6 +291,10 @@ causal_conv_tile_kernel(const float* __restrict__ x, long long ldx, const float*
             u[2] = fmaf(wt[2][j], win[j].z, u[2]);
             u[3] = fmaf(wt[3][j], win[j].w, u[3]);
         }
+        if (bias) {
+#pragma unroll
+            for (int e = 0; e < 4; e++) u[e] += bs[e];
+        }
         if (act == 1) {
 #pragma unroll
             for (int e = 0; e < 4; e++) u[e] = u[e] * sigmoid_f(u[e]);
@@ -293,12 +306,12 @@ causal_conv_tile_kernel(const float* __restrict__ x, long long ldx, const float*
 }
 
 template <int TAPS>
-static void causal_conv_tile_launch(const float* x, long long ldx, const float* w, const float* conv_state,
+static void causal_conv_tile_launch(const float* x, long long ldx, const float* w, const float* bias, const float* conv_state,
                                     long long state_stride, const int* tok_seq, const int* seq_start, const int* seq_slot,
                                     float* y, int n_rows, int C, int act, cudaStream_t stream) {
     esp_launch_pdl(ESP_PDL_SMALL, causal_conv_tile_kernel<TAPS>,
                    dim3((n_rows + CONV_TILE_ROWS - 1) / CONV_TILE_ROWS, (C / 4 + 63) / 64), dim3(64), 0, stream, x, ldx, w,
-                   conv_state, state_stride, tok_seq, seq_start, seq_slot, y, n_rows, C, act);
+                   bias, conv_state, state_stride, tok_seq, seq_start, seq_slot, y, n_rows, C, act);
 }
 
 // state[slot] <- the last taps - 1 inputs of the sequence after this step (a thread owns a channel: it reads what it
@@ -372,23 +385,23 @@ ESP_API int esp_channel_decay_prepare(float* z, const float* bias, float tau, co
 }
 
 // The convolution of a step's rows, then the sequences' convolution states.
-ESP_API int esp_causal_conv(const float* x, long long ldx, const float* w, float* conv_state, long long state_stride,
+ESP_API int esp_causal_conv(const float* x, long long ldx, const float* w, const float* bias, float* conv_state, long long state_stride,
                             const int* tok_seq, const int* seq_start, const int* seq_slot, float* y, int n_rows, int n_seqs,
                             int C, int taps, int act, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     if (taps < 1 || taps > CONV_MAX_TAPS || C <= 0) return (int)cudaErrorInvalidValue;
     // which form runs depends on the sizes and the buffers' alignment alone, never on the rows of a step
     const bool tiled = taps >= 2 && taps <= 4 && C % 4 == 0 && ldx % 4 == 0 && state_stride % 4 == 0 &&
-                       (((size_t)x | (size_t)conv_state | (size_t)y) & 15) == 0;
+                       (((size_t)x | (size_t)conv_state | (size_t)y) & 15) == 0;     // bias: scalar loads
 #define ESP_CONV_TILE(N)                                                                                               \
-    causal_conv_tile_launch<N>(x, ldx, w, (const float*)conv_state, state_stride, tok_seq, seq_start, seq_slot, y, n_rows, C, \
+    causal_conv_tile_launch<N>(x, ldx, w, bias, (const float*)conv_state, state_stride, tok_seq, seq_start, seq_slot, y, n_rows, C, \
                                act, stream)
     if (tiled && taps == 2) ESP_CONV_TILE(2);
     else if (tiled && taps == 3) ESP_CONV_TILE(3);
     else if (tiled) ESP_CONV_TILE(4);
     else
         esp_launch_pdl(ESP_PDL_SMALL, causal_conv_kernel, dim3(n_rows), dim3(C >= 1024 ? 256 : 128), 0, stream, x, ldx, w,
-                       (const float*)conv_state, state_stride, tok_seq, seq_start, seq_slot, y, C, taps, act);
+                       bias, (const float*)conv_state, state_stride, tok_seq, seq_start, seq_slot, y, C, taps, act);
 #undef ESP_CONV_TILE
     if (taps > 1)
         esp_launch_pdl(ESP_PDL_SMALL, causal_conv_keep_kernel, dim3(n_seqs, (C + 127) / 128), dim3(128), 0, stream, x, ldx,

@@ -397,6 +397,20 @@ int pick_vr(int H, const void* qx, const void* pool, void* out, const int* tok_s
     ESP_LA(16);
 #undef ESP_LA
 }
+// y[n, h, :] = o[n, h, :] * sigmoid(gate[n * ldg + h]): one number per token and head on the head's whole output.
+template <typename T>
+__global__ void head_scalar_gate_kernel(const float* __restrict__ o, const float* __restrict__ gate, long long ldg,
+                                        T* __restrict__ y, long long total, int H, int V) {
+    pdl_trigger();
+    pdl_wait();
+    for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total; idx += (long long)gridDim.x * blockDim.x) {
+        const long long nh = idx / V;
+        const long long n = nh / H;
+        const int h = (int)(nh - n * H);
+        const float g = gate[n * ldg + h];
+        y[idx] = from_f32<T>(o[idx] / (1.0f + expf(-g)));
+    }
+}
 }  // namespace
 
 ESP_API int esp_latent_kv_store(const float* d, const float* norm_w, const float* inv_freq, float mag, int rot_dims,
@@ -471,4 +485,19 @@ ESP_API int esp_attn_latent(const void* qx, const void* pool, void* out, int is_
                              window, scale, status, stream);
     return pick_vr<float>(H, qx, pool, out, tok_seq, tok_pos, block_table, table_stride, n_pages, page, n_tokens, hdk, hdv,
                           window, scale, status, stream);
+}
+
+ESP_API int esp_head_scalar_gate(const float* o, const float* gate, long long ldg, void* y, int y_is_bf16, int n_rows, int H,
+                                 int V, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    if (H <= 0 || V <= 0) return (int)cudaErrorInvalidValue;
+    const long long total = (long long)n_rows * H * V;
+    const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+    if (y_is_bf16)
+        esp_launch_pdl(ESP_PDL_SMALL, head_scalar_gate_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, o, gate, ldg, (bf16*)y,
+                       total, H, V);
+    else
+        esp_launch_pdl(ESP_PDL_SMALL, head_scalar_gate_kernel<float>, dim3(blocks), dim3(256), 0, stream, o, gate, ldg, (float*)y,
+                       total, H, V);
+    return esp_launch_status();
 }

@@ -45,6 +45,68 @@ __device__ __forceinline__ void scores_from_logits(const float* lg, float* ps, i
     }
 }
 
+// What a choice may depend on besides the scores: a number per expert that is added to the score for the choice only
+// (``correction``, may be null), and a limit to the best ``keep`` of ``n_groups`` equal groups of neighbouring experts
+// (a group's score is its largest corrected score; ties go to the lower group; n_groups <= 32, 0 or 1: no limit).
+struct RouteChoice {
+    const float* correction;
+    int n_groups;
+    int keep;
+};
+
+// One token's top-k by one warp.  ps[e]: its scores (left as they are when a correction or groups are given, else
+// the chosen entries are overwritten); cs: n_experts floats of scratch for the corrected scores.  The k experts with
+// the largest (corrected, group-limited) score win, ties to the lower id; lane r keeps rank r: its expert in my_e and
+// that expert's uncorrected score in my_p.  Returns the sum of the chosen scores.
+__device__ __forceinline__ float choose_topk(float* ps, float* cs, int n_experts, int top_k, int lane, RouteChoice ch,
+                                             float& my_p, int& my_e, bool& bad) {
+    float* sel = ps;
+    if (ch.correction || ch.n_groups > 1) {
+        sel = cs;
+        for (int e = lane; e < n_experts; e += 32) cs[e] = ps[e] + (ch.correction ? ch.correction[e] : 0.f);
+        __syncwarp();
+        if (ch.n_groups > 1) {
+            const int per = n_experts / ch.n_groups;
+            float gm = -INFINITY;
+            if (lane < ch.n_groups)
+                for (int e = lane * per; e < (lane + 1) * per; e++) gm = fmaxf(gm, cs[e]);
+            int ahead = 0;                                  // groups that come before this lane's
+            for (int g = 0; g < ch.n_groups; g++) {
+                const float o = __shfl_sync(0xffffffffu, gm, g);
+                if (o > gm || (o == gm && g < lane)) ahead++;
+            }
+            const unsigned kept = __ballot_sync(0xffffffffu, lane < ch.n_groups && ahead < ch.keep);
+            for (int e = lane; e < n_experts; e += 32)
+                if (!((kept >> (e / per)) & 1u)) cs[e] = -INFINITY;   // out of the running, whatever the sign of the scores
+            __syncwarp();
+        }
+    }
+    float mass = 0.f;
+    for (int r = 0; r < top_k; r++) {
+        float best = -INFINITY;
+        int best_e = 0x7fffffff;
+        for (int e = lane; e < n_experts; e += 32) {
+            const float p = sel[e];
+            if (!(p == p) || p == INFINITY) bad = true;
+            if (p > best) { best = p; best_e = e; }       // ascending e per lane: the first maximum is the lowest id
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+            if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
+        }
+        if (best_e == 0x7fffffff) { best_e = 0; bad = true; }
+        const float score = sel == ps ? best : ps[best_e];
+        __syncwarp();
+        if (lane == 0) sel[best_e] = -INFINITY;           // taken out of the running
+        if (lane == r) { my_p = score; my_e = best_e; }   // top_k <= 32: rank r is kept by lane r
+        mass += score;
+        __syncwarp();
+    }
+    return mass;
+}
+
 // A lane's share of dot(hs[t], w) for TPB token rows at once: 4 consecutive
 // weights at a time (8-byte loads of bfloat16, 16-byte of float), lanes
 // interleaved so that the float4 reads of hs fall into distinct banks, several
@@ -92,10 +154,11 @@ __global__ void __launch_bounds__(ROUTER_THREADS)
 router_topk_kernel(const TH* __restrict__ h, const TW* __restrict__ w_router, const TW* __restrict__ w_gate,
                    int* __restrict__ topk_ids, float* __restrict__ topk_w, float* __restrict__ gate,
                    float* __restrict__ probs_out, int n_tokens, int width, int n_experts, int top_k, int norm_topk,
-                   int* __restrict__ status) {
+                   RouteChoice choice, int* __restrict__ status) {
     extern __shared__ float smem[];
     float* hs = smem;                          // [TPB][width]
     float* ps_all = smem + TPB * width;        // [TPB][n_experts]
+    float* cs_all = ps_all + TPB * n_experts;  // [TPB][n_experts]
     const int n0 = blockIdx.x * TPB, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarp = ROUTER_THREADS / 32;
     const int live = min(TPB, n_tokens - n0);
     for (int i = tid; i < TPB * width; i += ROUTER_THREADS) {
@@ -169,30 +232,10 @@ router_topk_kernel(const TH* __restrict__ h, const TW* __restrict__ w_router, co
         float* ps = ps_all + t * n_experts;
         scores_from_logits(ps, ps, n_experts, lane, norm_topk & ROUTE_SIGMOID, probs_out ? probs_out + (size_t)n * n_experts : nullptr);
         __syncwarp();
-        // top-k by repeated arg-max (k and E are small); ties go to the lower id; rank r is kept by lane r
         bool bad = false;
-        float mass = 0.f, my_p = 0.f;
+        float my_p = 0.f;
         int my_e = 0;
-        for (int r = 0; r < top_k; r++) {
-            float best = -INFINITY;
-            int best_e = 0x7fffffff;
-            for (int e = lane; e < n_experts; e += 32) {
-                const float p = ps[e];
-                if (!(p == p) || isinf(p)) bad = true;
-                if (p > best) { best = p; best_e = e; }   // ascending e per lane: the first maximum is the lowest id
-            }
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) {
-                const float ob = __shfl_xor_sync(0xffffffffu, best, o);
-                const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
-                if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
-            }
-            if (best_e == 0x7fffffff) { best_e = 0; bad = true; }
-            if (lane == 0) ps[best_e] = -1.0f;            // probabilities are >= 0: taken out of the running
-            if (lane == r) { my_p = best; my_e = best_e; }
-            mass += best;
-            __syncwarp();
-        }
+        const float mass = choose_topk(ps, cs_all + t * n_experts, n_experts, top_k, lane, choice, my_p, my_e, bad);
         const float denom = (norm_topk & ROUTE_RENORM) ? mass : 1.0f;
         if (__any_sync(0xffffffffu, bad) || !(denom > 0.f)) {
             if (lane == 0) atomicOr(status, ESP_STATUS_ROUTER_NONFINITE);
@@ -302,39 +345,20 @@ router_logits_mma_kernel(const float* __restrict__ h, const bf16* __restrict__ w
 __global__ void __launch_bounds__(256)
 router_select_kernel(const float* __restrict__ logits, int* __restrict__ topk_ids, float* __restrict__ topk_w,
                      float* __restrict__ gate, float* __restrict__ probs_out, int n_tokens, int n_experts, int top_k,
-                     int norm_topk, int has_gate, int* __restrict__ status) {
-    extern __shared__ float sel_ps[];                               // [8 warps][n_experts]
+                     int norm_topk, int has_gate, RouteChoice choice, int* __restrict__ status) {
+    extern __shared__ float sel_ps[];                               // [8 warps][2 * n_experts]: scores, corrected scores
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int n = blockIdx.x * 8 + warp;
     if (n >= n_tokens) return;
-    float* ps = sel_ps + warp * n_experts;
+    float* ps = sel_ps + warp * 2 * n_experts;
     const float* lg = logits + (size_t)n * (n_experts + 1);
     scores_from_logits(lg, ps, n_experts, lane, norm_topk & ROUTE_SIGMOID, probs_out ? probs_out + (size_t)n * n_experts : nullptr);
     if (lane == 0 && has_gate) gate[n] = 1.0f / (1.0f + expf(-lg[n_experts]));
     __syncwarp();
     bool bad = false;
-    float mass = 0.f, my_p = 0.f;
+    float my_p = 0.f;
     int my_e = 0;
-    for (int r = 0; r < top_k; r++) {
-        float best = -INFINITY;
-        int best_e = 0x7fffffff;
-        for (int e = lane; e < n_experts; e += 32) {
-            const float p = ps[e];
-            if (!(p == p) || isinf(p)) bad = true;
-            if (p > best) { best = p; best_e = e; }           // ascending e per lane: the first maximum is the lowest id
-        }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
-            const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
-            if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
-        }
-        if (best_e == 0x7fffffff) { best_e = 0; bad = true; }
-        if (lane == 0) ps[best_e] = -1.0f;
-        if (lane == r) { my_p = best; my_e = best_e; }
-        mass += best;
-        __syncwarp();
-    }
+    const float mass = choose_topk(ps, ps + n_experts, n_experts, top_k, lane, choice, my_p, my_e, bad);
     const float denom = (norm_topk & ROUTE_RENORM) ? mass : 1.0f;
     if (__any_sync(0xffffffffu, bad) || !(denom > 0.f)) {
         if (lane == 0) atomicOr(status, ESP_STATUS_ROUTER_NONFINITE);
@@ -377,50 +401,31 @@ router_logits_kernel(const TH* __restrict__ h, const TW* __restrict__ w_router, 
 __global__ void __launch_bounds__(256)
 route_small_kernel(const float* __restrict__ logits, int* __restrict__ topk_ids, float* __restrict__ topk_w,
                    float* __restrict__ gate, float* __restrict__ probs_out, int n_tokens, int n_experts, int top_k,
-                   int norm_topk, int has_gate, int* __restrict__ offsets, int* __restrict__ perm_token,
+                   int norm_topk, int has_gate, RouteChoice choice, int n_real, int* __restrict__ offsets, int* __restrict__ perm_token,
                    float* __restrict__ perm_weight, int* __restrict__ inverse, int* __restrict__ status,
                    unsigned long long* __restrict__ distinct, int* __restrict__ tile_group, int* __restrict__ tile_row0,
                    int* __restrict__ tile_count, int* __restrict__ n_tiles) {
     pdl_trigger();
     pdl_wait();
     extern __shared__ float sm_f[];
-    float* ps_all = sm_f;                                      // [8 warps][n_experts]
-    int* counts = reinterpret_cast<int*>(sm_f + 8 * n_experts); // [n_experts]
+    float* ps_all = sm_f;                                      // [8 warps][2 * n_experts]: scores, corrected scores
+    int* counts = reinterpret_cast<int*>(sm_f + 16 * n_experts); // [n_experts]
     int* cursor = counts + n_experts;                           // [n_experts + 1]
     int* pair_e = cursor + n_experts + 1;                       // [n_tokens * top_k]
     float* pair_w = reinterpret_cast<float*>(pair_e + n_tokens * top_k);   // [n_tokens * top_k]
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     for (int e = tid; e < n_experts; e += 256) counts[e] = 0;
     __syncthreads();
-    float* ps = ps_all + warp * n_experts;
+    float* ps = ps_all + warp * 2 * n_experts;
     for (int n = warp; n < n_tokens; n += 8) {
         const float* lg = logits + (size_t)n * (n_experts + 1);
         scores_from_logits(lg, ps, n_experts, lane, norm_topk & ROUTE_SIGMOID, probs_out ? probs_out + (size_t)n * n_experts : nullptr);
         if (lane == 0 && has_gate) gate[n] = 1.0f / (1.0f + expf(-lg[n_experts]));
         __syncwarp();
         bool bad = false;
-        float mass = 0.f, my_p = 0.f;
+        float my_p = 0.f;
         int my_e = 0;
-        for (int r = 0; r < top_k; r++) {
-            float best = -INFINITY;
-            int best_e = 0x7fffffff;
-            for (int e = lane; e < n_experts; e += 32) {
-                const float p = ps[e];
-                if (!(p == p) || isinf(p)) bad = true;
-                if (p > best) { best = p; best_e = e; }
-            }
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) {
-                const float ob = __shfl_xor_sync(0xffffffffu, best, o);
-                const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
-                if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
-            }
-            if (best_e == 0x7fffffff) { best_e = 0; bad = true; }
-            if (lane == 0) ps[best_e] = -1.0f;
-            if (lane == r) { my_p = best; my_e = best_e; }       // top_k <= 32: rank r is kept by lane r
-            mass += best;
-            __syncwarp();
-        }
+        const float mass = choose_topk(ps, ps + n_experts, n_experts, top_k, lane, choice, my_p, my_e, bad);
         const float denom = (norm_topk & ROUTE_RENORM) ? mass : 1.0f;
         if (__any_sync(0xffffffffu, bad) || !(denom > 0.f)) {
             if (lane == 0) atomicOr(status, ESP_STATUS_ROUTER_NONFINITE);
@@ -431,7 +436,7 @@ route_small_kernel(const float* __restrict__ logits, int* __restrict__ topk_ids,
             topk_w[(size_t)n * top_k + lane] = w;
             pair_e[n * top_k + lane] = my_e;                      // kept in shared memory for the placement below
             pair_w[n * top_k + lane] = w;
-            atomicAdd(&counts[my_e], 1);
+            if (my_e < n_real) atomicAdd(&counts[my_e], 1);    // experts from n_real on have no rows of their own
         }
         __syncwarp();
     }
@@ -475,12 +480,16 @@ route_small_kernel(const float* __restrict__ logits, int* __restrict__ topk_ids,
     const int n_pairs = n_tokens * top_k;
     for (int i = tid; i < n_pairs; i += 256) {
         const int e = pair_e[i];
+        if (e >= n_real) { inverse[i] = -1; continue; }
         const int row = atomicAdd(&cursor[e], 1);
         perm_token[row] = i / top_k;
         perm_weight[row] = pair_w[i];
         inverse[i] = row;
     }
 }
+
+// ids from n_experts up to n_ids name experts without rows (their pairs get inverse -1); anything else is an error
+__device__ __forceinline__ bool e_bad(int e, int n_ids) { return e < 0 || e >= n_ids; }
 
 // The same for many pairs: every warp of the one block counts into a table of its own, so that an expert
 // that takes most of the tokens is not one address that a thousand threads add to in turn; a scan over
@@ -491,7 +500,7 @@ moe_permute_wide_kernel(const int* __restrict__ topk_ids, const float* __restric
                         int* __restrict__ offsets, int* __restrict__ perm_token, float* __restrict__ perm_weight,
                         int* __restrict__ inverse, int top_k, int* __restrict__ tile_group, int* __restrict__ tile_row0,
                         int* __restrict__ tile_count, int* __restrict__ n_tiles, int tile_rows, int max_tiles,
-                        int* __restrict__ status, unsigned long long* __restrict__ distinct) {
+                        int* __restrict__ status, unsigned long long* __restrict__ distinct, int n_ids) {
     extern __shared__ int sm[];
     int* hist = sm;                                  // [32][n_experts]: counts, later each warp's next row
     int* offs = sm + 32 * n_experts;                 // [n_experts + 1]
@@ -512,12 +521,12 @@ moe_permute_wide_kernel(const int* __restrict__ topk_ids, const float* __restric
     for (int j = 0; j < PER; j++) {
         if (held[j] == -2) continue;
         if (held[j] >= 0 && held[j] < n_experts) atomicAdd(&mine[held[j]], 1);
-        else atomicOr(status, ESP_STATUS_BAD_INDEX);
+        else if (e_bad(held[j], n_ids)) atomicOr(status, ESP_STATUS_BAD_INDEX);
     }
     for (int i = tid + PER * 1024; i < n_pairs; i += 1024) {
         const int e = topk_ids[i];
         if (e >= 0 && e < n_experts) atomicAdd(&mine[e], 1);
-        else atomicOr(status, ESP_STATUS_BAD_INDEX);
+        else if (e_bad(e, n_ids)) atomicOr(status, ESP_STATUS_BAD_INDEX);
     }
     __syncthreads();
     // thread e: the expert's total, and every warp's count turned into its share's first row within the expert
@@ -591,7 +600,7 @@ moe_permute_kernel(const int* __restrict__ topk_ids, const float* __restrict__ t
                    int* __restrict__ offsets, int* __restrict__ perm_token, float* __restrict__ perm_weight,
                    int* __restrict__ inverse, int top_k, int* __restrict__ tile_group, int* __restrict__ tile_row0,
                    int* __restrict__ tile_count, int* __restrict__ n_tiles, int tile_rows, int max_tiles,
-                   int* __restrict__ status, unsigned long long* __restrict__ distinct) {
+                   int* __restrict__ status, unsigned long long* __restrict__ distinct, int n_ids) {
     extern __shared__ int sm[];
     int* counts = sm;                      // [n_experts]
     int* cursor = sm + n_experts;          // [n_experts + 1]
@@ -600,7 +609,7 @@ moe_permute_kernel(const int* __restrict__ topk_ids, const float* __restrict__ t
     for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) {
         const int e = topk_ids[i];
         if (e >= 0 && e < n_experts) atomicAdd(&counts[e], 1);
-        else atomicOr(status, ESP_STATUS_BAD_INDEX);
+        else if (e_bad(e, n_ids)) atomicOr(status, ESP_STATUS_BAD_INDEX);
     }
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -639,13 +648,16 @@ moe_permute_kernel(const int* __restrict__ topk_ids, const float* __restrict__ t
 
 // y[t, :] = sum over the token's chosen experts, in ascending expert id, of
 // expert_out[inverse[t, r], :] (already scaled by the routing weight), then
-// + gate[t] * shared[t, :].
+// + gate[t] * shared[t, :].  With ``ident`` (float [tokens, width]): a chosen id from n_real on is an expert without
+// weights whose output is its input; it adds topk_w[t, r] * ident[t, :] in its place in the order.
 __global__ void moe_combine_kernel(const float* __restrict__ expert_out, const int* __restrict__ topk_ids,
                                    const int* __restrict__ inverse, const float* __restrict__ gate,
-                                   const float* __restrict__ shared, float* __restrict__ y, int width, int top_k) {
+                                   const float* __restrict__ shared, float* __restrict__ y, int width, int top_k,
+                                   const float* __restrict__ topk_w, const float* __restrict__ ident, int n_real) {
     pdl_trigger();
     pdl_wait();
     __shared__ int order[MAX_TOPK];
+    __shared__ float pass_w[MAX_TOPK];
     const int t = blockIdx.x;
     if (threadIdx.x == 0) {
         int ids[MAX_TOPK];
@@ -656,7 +668,11 @@ __global__ void moe_combine_kernel(const float* __restrict__ expert_out, const i
             while (b >= 0 && ids[order[b]] > ia) { order[b + 1] = order[b]; b--; }
             order[b + 1] = oa;
         }
-        for (int r = 0; r < top_k; r++) order[r] = inverse[(size_t)t * top_k + order[r]];
+        for (int r = 0; r < top_k; r++) {
+            const int o = order[r];
+            pass_w[r] = (ident && ids[o] >= n_real) ? topk_w[(size_t)t * top_k + o] : 0.f;
+            order[r] = inverse[(size_t)t * top_k + o];
+        }
     }
     __syncthreads();
     const float g = gate ? gate[t] : 1.0f;       // no gate: the shared rows are added as they are
@@ -669,6 +685,10 @@ __global__ void moe_combine_kernel(const float* __restrict__ expert_out, const i
                 if (row >= 0) {
                     const float4 v = *reinterpret_cast<const float4*>(expert_out + (size_t)row * width + i);
                     acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+                } else if (pass_w[r] != 0.f) {
+                    const float4 v = *reinterpret_cast<const float4*>(ident + (size_t)t * width + i);
+                    const float pw = pass_w[r];
+                    acc.x += pw * v.x; acc.y += pw * v.y; acc.z += pw * v.z; acc.w += pw * v.w;
                 }
             }
             if (shared) {
@@ -684,6 +704,7 @@ __global__ void moe_combine_kernel(const float* __restrict__ expert_out, const i
         for (int r = 0; r < top_k; r++) {
             const int row = order[r];
             if (row >= 0) acc += expert_out[(size_t)row * width + i];
+            else if (pass_w[r] != 0.f) acc += pass_w[r] * ident[(size_t)t * width + i];
         }
         if (shared) acc += g * shared[(size_t)t * width + i];
         y[(size_t)t * width + i] = acc;
@@ -700,7 +721,8 @@ moe_combine_add_rmsnorm_kernel(const float* __restrict__ expert_out, const int* 
                                const int* __restrict__ inverse, const float* __restrict__ gate,
                                const float* __restrict__ shared, float* __restrict__ x, const float* __restrict__ gamma,
                                const int* __restrict__ rows, TH* __restrict__ h, float* __restrict__ h32, int width,
-                               int top_k, float eps, int write_x, int early) {
+                               int top_k, float eps, int write_x, int early, const float* __restrict__ topk_w,
+                               const float* __restrict__ ident, int n_real) {
     pdl_trigger();
     // The kernel before this one in the stream made the experts' rows or the shared expert's row.  It lets this one
     // be set up only behind its own wait (the grouped product gives its signal when its weights are in), and by then
@@ -708,6 +730,7 @@ moe_combine_add_rmsnorm_kernel(const float* __restrict__ expert_out, const int* 
     // the wait, while that kernel finishes.  ``early`` 0 (every grouped product a dependent launch): everything waits.
     if (!early) pdl_wait();
     __shared__ int order[MAX_TOPK];
+    __shared__ float pass_w[MAX_TOPK];          // weight of a chosen expert without weights (its output is its input), else 0
     __shared__ float scratch[33];
     const int r = blockIdx.x;
     const size_t t = rows ? (size_t)rows[r] : (size_t)r;
@@ -720,7 +743,11 @@ moe_combine_add_rmsnorm_kernel(const float* __restrict__ expert_out, const int* 
             while (b >= 0 && ids[order[b]] > ia) { order[b + 1] = order[b]; b--; }
             order[b + 1] = oa;
         }
-        for (int j = 0; j < top_k; j++) order[j] = inverse[t * top_k + order[j]];
+        for (int j = 0; j < top_k; j++) {
+            const int o = order[j];
+            pass_w[j] = (ident && ids[o] >= n_real) ? topk_w[t * top_k + o] : 0.f;
+            order[j] = inverse[t * top_k + o];
+        }
     }
     const float g = gate ? gate[t] : 1.0f;       // no gate: the shared rows are added as they are
     const int pieces = width / 4;
@@ -743,6 +770,10 @@ moe_combine_add_rmsnorm_kernel(const float* __restrict__ expert_out, const int* 
                 if (row >= 0) {
                     const float4 e = reinterpret_cast<const float4*>(expert_out + (size_t)row * width)[q];
                     acc.x += e.x; acc.y += e.y; acc.z += e.z; acc.w += e.w;
+                } else if (pass_w[j] != 0.f) {
+                    const float4 e = reinterpret_cast<const float4*>(ident + t * width)[q];
+                    const float pw = pass_w[j];
+                    acc.x += pw * e.x; acc.y += pw * e.y; acc.z += pw * e.z; acc.w += pw * e.w;
                 }
             }
             if (shared) {
@@ -779,12 +810,17 @@ moe_combine_add_rmsnorm_kernel(const float* __restrict__ expert_out, const int* 
 // weights, many tokens and a width that is a multiple of 128, the logits are made on the tensor cores.
 ESP_API int esp_router_topk(const void* h, int h_is_bf16, const void* w_router, const void* w_gate, int w_is_bf16,
                             int* topk_ids, float* topk_w, float* gate, float* probs_out, float* logits, int n_tokens,
-                            int width, int n_experts, int top_k, int norm_topk, int* status, cudaStream_t stream) {
+                            int width, int n_experts, int top_k, int norm_topk, const float* correction, int n_groups,
+                            int keep_groups, int* status, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (top_k > MAX_TOPK || top_k <= 0 || top_k > n_experts) return (int)cudaErrorInvalidValue;
+    if (n_groups > 32 || (n_groups > 1 && (n_experts % n_groups != 0 || keep_groups < 1 || keep_groups > n_groups ||
+                                           keep_groups * (n_experts / n_groups) < top_k)))
+        return (int)cudaErrorInvalidValue;
+    const RouteChoice choice{correction, n_groups, keep_groups};
     const int rows = n_experts + (w_gate ? 1 : 0);
     if (logits && !h_is_bf16 && w_is_bf16 && n_tokens >= 64 && width % 128 == 0 && rows <= 72 &&
-        (size_t)8 * n_experts * sizeof(float) <= 48 * 1024 && (reinterpret_cast<uintptr_t>(h) & 15) == 0 &&
+        (size_t)16 * n_experts * sizeof(float) <= 48 * 1024 && (reinterpret_cast<uintptr_t>(h) & 15) == 0 &&
         (reinterpret_cast<uintptr_t>(w_router) & 7) == 0 && (!w_gate || (reinterpret_cast<uintptr_t>(w_gate) & 7) == 0)) {
         const int blocks = (n_tokens + 15) / 16;
 #define ESP_ROUTER_MMA(NT, KW)                                                                                         \
@@ -798,14 +834,14 @@ ESP_API int esp_router_topk(const void* h, int h_is_bf16, const void* w_router, 
             else ESP_ROUTER_MMA(9, 4);
         }
 #undef ESP_ROUTER_MMA
-        router_select_kernel<<<(n_tokens + 7) / 8, 256, (size_t)8 * n_experts * sizeof(float), stream>>>(
-            logits, topk_ids, topk_w, gate, probs_out, n_tokens, n_experts, top_k, norm_topk, w_gate ? 1 : 0, status);
+        router_select_kernel<<<(n_tokens + 7) / 8, 256, (size_t)16 * n_experts * sizeof(float), stream>>>(
+            logits, topk_ids, topk_w, gate, probs_out, n_tokens, n_experts, top_k, norm_topk, w_gate ? 1 : 0, choice, status);
         return esp_launch_status();
     }
     // many tokens: four or eight per block, so that the router's weights are fetched that much less often
     int tpb = n_tokens > 256 ? 8 : n_tokens > 32 ? 4 : 1;
-    if ((size_t)tpb * (width + n_experts) * sizeof(float) > 200 * 1024) tpb = 1;
-    const size_t smem = (size_t)tpb * (width + n_experts) * sizeof(float);
+    if ((size_t)tpb * (width + 2 * n_experts) * sizeof(float) > 200 * 1024) tpb = 1;
+    const size_t smem = (size_t)tpb * (width + 2 * n_experts) * sizeof(float);
     if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
     const int blocks = (n_tokens + tpb - 1) / tpb;
 #define ESP_ROUTER(TH, TW, TPB)                                                                                       \
@@ -814,7 +850,7 @@ ESP_API int esp_router_topk(const void* h, int h_is_bf16, const void* w_router, 
             cudaFuncSetAttribute(router_topk_kernel<TH, TW, TPB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
         router_topk_kernel<TH, TW, TPB><<<blocks, ROUTER_THREADS, smem, stream>>>(                                     \
             (const TH*)h, (const TW*)w_router, (const TW*)w_gate, topk_ids, topk_w, gate, probs_out, n_tokens, width, \
-            n_experts, top_k, norm_topk, status);                                                                     \
+            n_experts, top_k, norm_topk, choice, status);                                                                     \
     } while (0)
 #define ESP_ROUTER_T(TH, TW)                                                                                          \
     do {                                                                                                              \
@@ -838,14 +874,20 @@ ESP_API int esp_route_small(const void* h, int h_is_bf16, const void* w_router, 
                             float* logits, int* topk_ids, float* topk_w, float* gate, float* probs_out, int n_tokens,
                             int width, int n_experts, int top_k, int norm_topk, int* offsets, int* perm_token,
                             float* perm_weight, int* inverse, int* status, unsigned long long* distinct, int* tile_group,
-                            int* tile_row0, int* tile_count, int* n_tiles, int max_tiles, cudaStream_t stream) {
+                            int* tile_row0, int* tile_count, int* n_tiles, int max_tiles, const float* correction,
+                            int n_groups, int keep_groups, int n_real, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (top_k > MAX_TOPK || top_k <= 0 || top_k > n_experts || n_tokens > ROUTE_SMALL_MAX) return (int)cudaErrorInvalidValue;
-    // the tile list (all four or none): one tile per expert with rows
-    if (tile_group && (!tile_row0 || !tile_count || !n_tiles || max_tiles < (n_experts < n_tokens * top_k ? n_experts : n_tokens * top_k)))
+    if (n_real <= 0 || n_real > n_experts || n_groups > 32 ||
+        (n_groups > 1 && (n_experts % n_groups != 0 || keep_groups < 1 || keep_groups > n_groups ||
+                          keep_groups * (n_experts / n_groups) < top_k)))
+        return (int)cudaErrorInvalidValue;
+    const RouteChoice choice{correction, n_groups, keep_groups};
+    // the tile list (all four or none): one tile per expert with rows (experts from n_real on have none)
+    if (tile_group && (!tile_row0 || !tile_count || !n_tiles || max_tiles < (n_real < n_tokens * top_k ? n_real : n_tokens * top_k)))
         return (int)cudaErrorInvalidValue;
     const size_t smem_a = (size_t)width * sizeof(float);
-    const size_t smem_b = (size_t)(8 * n_experts) * sizeof(float) + (size_t)(2 * n_experts + 1) * sizeof(int) +
+    const size_t smem_b = (size_t)(16 * n_experts) * sizeof(float) + (size_t)(2 * n_experts + 1) * sizeof(int) +
                           (size_t)n_tokens * top_k * (sizeof(int) + sizeof(float));
     if (smem_a > 48 * 1024 || smem_b > 48 * 1024) return (int)cudaErrorInvalidValue;
     const dim3 grid(n_tokens, (n_experts + 1 + 7) / 8);
@@ -858,7 +900,7 @@ ESP_API int esp_route_small(const void* h, int h_is_bf16, const void* w_router, 
     else ESP_LOGITS(float, float);
 #undef ESP_LOGITS
     esp_launch_pdl(ESP_PDL_SMALL, route_small_kernel, dim3(1), dim3(256), smem_b, stream, logits, topk_ids, topk_w, gate, probs_out, n_tokens, n_experts, top_k,
-                                                   norm_topk, w_gate ? 1 : 0, offsets, perm_token, perm_weight, inverse,
+                                                   norm_topk, w_gate ? 1 : 0, choice, n_real, offsets, perm_token, perm_weight, inverse,
                                                    status, distinct, tile_group, tile_row0, tile_count, n_tiles);
     return esp_launch_status();
 }
@@ -870,37 +912,40 @@ ESP_API int esp_route_small(const void* h, int h_is_bf16, const void* w_router, 
 ESP_API int esp_moe_permute(const int* topk_ids, const float* topk_w, int n_tokens, int top_k, int n_experts,
                             int* offsets, int* perm_token, float* perm_weight, int* inverse, int* tile_group,
                             int* tile_row0, int* tile_count, int* n_tiles, int tile_rows, int max_tiles, int* status,
-                            unsigned long long* distinct, cudaStream_t stream) {
+                            unsigned long long* distinct, int n_ids, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
+    if (n_ids < n_experts) n_ids = n_experts;       // ids from n_experts up to n_ids name experts without rows
     const size_t smem = (size_t)(2 * n_experts + 1) * sizeof(int);
     if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;
     const size_t smem_wide = (size_t)(33 * n_experts + 1) * sizeof(int);
     if (n_tokens * top_k >= 2048 && smem_wide <= 48 * 1024) {
         moe_permute_wide_kernel<<<1, 1024, smem_wide, stream>>>(topk_ids, topk_w, n_tokens * top_k, n_experts, offsets,
                                                                 perm_token, perm_weight, inverse, top_k, tile_group, tile_row0,
-                                                                tile_count, n_tiles, tile_rows, max_tiles, status, distinct);
+                                                                tile_count, n_tiles, tile_rows, max_tiles, status, distinct, n_ids);
         return esp_launch_status();
     }
     moe_permute_kernel<<<1, 1024, smem, stream>>>(topk_ids, topk_w, n_tokens * top_k, n_experts, offsets, perm_token,
                                                   perm_weight, inverse, top_k, tile_group, tile_row0, tile_count, n_tiles,
-                                                  tile_rows, max_tiles, status, distinct);
+                                                  tile_rows, max_tiles, status, distinct, n_ids);
     return esp_launch_status();
 }
 
 ESP_API int esp_moe_combine(const float* expert_out, const int* topk_ids, const int* inverse, const float* gate,
-                            const float* shared, float* y, int n_tokens, int width, int top_k, cudaStream_t stream) {
+                            const float* shared, float* y, int n_tokens, int width, int top_k, const float* topk_w,
+                            const float* ident, int n_real, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
-    if (top_k > MAX_TOPK) return (int)cudaErrorInvalidValue;
-    esp_launch_pdl(ESP_PDL_SMALL, moe_combine_kernel, dim3(n_tokens), dim3(256), 0, stream, expert_out, topk_ids, inverse, gate, shared, y, width, top_k);
+    if (top_k > MAX_TOPK || (ident && !topk_w)) return (int)cudaErrorInvalidValue;
+    esp_launch_pdl(ESP_PDL_SMALL, moe_combine_kernel, dim3(n_tokens), dim3(256), 0, stream, expert_out, topk_ids, inverse, gate, shared, y, width, top_k,
+                   topk_w, ident, n_real);
     return esp_launch_status();
 }
 
 ESP_API int esp_moe_combine_add_rmsnorm(const float* expert_out, const int* topk_ids, const int* inverse, const float* gate,
                                         const float* shared, float* x, const float* gamma, const int* rows, void* h,
                                         int h_is_bf16, float* h32, int n_rows, int width, int top_k, float eps, int write_x,
-                                        cudaStream_t stream) {
+                                        const float* topk_w, const float* ident, int n_real, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
-    if (top_k > MAX_TOPK || width % 4 != 0 || width > 16384) return (int)cudaErrorInvalidValue;
+    if (top_k > MAX_TOPK || width % 4 != 0 || width > 16384 || (ident && !topk_w)) return (int)cudaErrorInvalidValue;
     int threads = ((width / 4 + 3) / 4 + 31) / 32 * 32;
     // one piece per thread while a block can hold them: a row's sum then has the same order whatever else is in the
     // step (the 32-bit path relies on it).  Many rows rounded to bfloat16: four pieces per thread, smaller blocks,
@@ -909,10 +954,10 @@ ESP_API int esp_moe_combine_add_rmsnorm(const float* expert_out, const int* topk
     const int early = esp_pdl_enabled(ESP_PDL_GROUPED) ? 0 : 1;
     if (h_is_bf16)
         esp_launch_pdl(ESP_PDL_SMALL, moe_combine_add_rmsnorm_kernel<bf16>, dim3(n_rows), dim3(threads), 0, stream, expert_out, topk_ids, inverse, gate, shared, x, gamma,
-                                                                            rows, (bf16*)h, h32, width, top_k, eps, write_x, early);
+                                                                            rows, (bf16*)h, h32, width, top_k, eps, write_x, early, topk_w, ident, n_real);
     else
         esp_launch_pdl(ESP_PDL_SMALL, moe_combine_add_rmsnorm_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, expert_out, topk_ids, inverse, gate, shared, x,
                                                                              gamma, rows, (float*)h, h32, width, top_k, eps,
-                                                                             write_x, early);
+                                                                             write_x, early, topk_w, ident, n_real);
     return esp_launch_status();
 }

@@ -68,18 +68,23 @@ _SIGNATURES = {
                        c_int, c_int, c_int, P],
     "esp_delta_prepare": [P, c_longlong, c_int, c_int, c_float, c_float, P, c_longlong, P, P, P, P, c_longlong, P, c_int, c_int, P],
     "esp_channel_decay_prepare": [P, P, c_float, P, c_longlong, c_float, P, c_longlong, c_int, P],
-    "esp_causal_conv": [P, c_longlong, P, P, c_longlong, P, P, P, P, c_int, c_int, c_int, c_int, c_int, P],
-    "esp_router_topk": [P, c_int, P, P, c_int, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, P, P],
-    "esp_moe_permute": [P, P, c_int, c_int, c_int, P, P, P, P, P, P, P, P, c_int, c_int, P, P, P],
+    "esp_selective_scan": [P, c_longlong, P, c_longlong, P, c_longlong, P, c_longlong, P, P, P, c_longlong, P, P, P, c_int, c_int,
+                           c_int, c_int, P],
+    "esp_head_scalar_gate": [P, P, c_longlong, P, c_int, c_int, c_int, c_int, P],
+    "esp_pair_rope_unitnorm_kvwrite": [P, P, P, c_int, c_float, c_int, P, c_int, P, P, P, P, P, P, c_int, P, c_int, c_int, c_int,
+                                       c_int, c_int, c_int, c_int, c_int, c_int, P, P],
+    "esp_causal_conv": [P, c_longlong, P, P, P, c_longlong, P, P, P, P, c_int, c_int, c_int, c_int, c_int, P],
+    "esp_router_topk": [P, c_int, P, P, c_int, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, P, c_int, c_int, P, P],
+    "esp_moe_permute": [P, P, c_int, c_int, c_int, P, P, P, P, P, P, P, P, c_int, c_int, P, P, c_int, P],
     "esp_gather_rows": [P, P, P, c_int, c_int, P],
     "esp_route_small": [P, c_int, P, P, c_int, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, P, P, P, P, P, P, P, P, P, P,
-                        c_int, P],
+                        c_int, P, c_int, c_int, c_int, P],
     "esp_gemm_tc05": [P, c_longlong, P, c_int, c_int, P, P, c_longlong, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int,
                       c_int, c_int, P, P],
     "esp_wait_probe": [c_int, P, P],
-    "esp_moe_combine": [P, P, P, P, P, P, c_int, c_int, c_int, P],
+    "esp_moe_combine": [P, P, P, P, P, P, c_int, c_int, c_int, P, P, c_int, P],
     "esp_pick_tokens": [P, c_int, c_int, P, P, P, P, P, P],
-    "esp_moe_combine_add_rmsnorm": [P, P, P, P, P, P, P, P, P, c_int, P, c_int, c_int, c_int, c_float, c_int, P],
+    "esp_moe_combine_add_rmsnorm": [P, P, P, P, P, P, P, P, P, c_int, P, c_int, c_int, c_int, c_float, c_int, P, P, c_int, P],
     "esp_gemm_skinny": [P, c_longlong, P, P, c_longlong, P, P, c_int, c_longlong, P, c_int, c_int, c_int, c_int, c_int,
                         c_int, c_int, P, P],
     "esp_qkv_rope_skinny": [P, c_longlong, P, P, P, P, P, P, c_int, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int,
@@ -369,17 +374,31 @@ def attn_simt(q, k_cache, v_cache, out, tok_seq, tok_pos, block_table, page, nh,
         int(chunk or 0), _ptr(status, torch.int32), _stream()), "attn_simt")
 
 
+def _choice_args(choice, n_experts):
+    """(correction pointer, groups, kept groups) of a ``choice`` = (correction float32 [experts] or None, groups, keep)."""
+    if choice is None:
+        return None, 0, 0
+    correction, groups, keep = choice
+    if correction is not None and correction.shape[0] != n_experts:
+        raise Backend("router: the correction has another length than the router has outputs")
+    if groups and groups > 1 and (groups > 32 or n_experts % groups or not 1 <= keep <= groups):
+        raise Backend(f"router: {groups} groups (keep {keep}) over {n_experts} experts are not taken")
+    return _ptr(correction, torch.float32, "correction"), int(groups or 0), int(keep or 0)
+
+
 def router_topk(h, w_router, w_gate, topk_ids, topk_w, gate, top_k, norm_topk, status, probs_out=None, logits=None,
-                sigmoid=False):
-    """``logits``: optional float32 scratch [n, experts + 1]; with it, 32-bit activations and bfloat16 weights
+                sigmoid=False, choice=None):
+    """``choice``: None, or (correction, groups, keep): a number per expert added to its score for the choice only, and
+    a limit of the choice to the best ``keep`` of ``groups`` equal groups of neighbouring experts.  ``logits``: optional float32 scratch [n, experts + 1]; with it, 32-bit activations and bfloat16 weights
     the logits of a step of many tokens are made on the tensor cores (three bfloat16 parts of every
     activation: products exact, sums in float)."""
     n, width = h.shape
     n_experts = w_router.shape[0]
     if top_k > 32:
         raise Backend(f"router: top-k {top_k} is beyond the 32 this kernel takes")
-    if (width + n_experts) * 4 > 200 * 1024:
+    if (width + 2 * n_experts) * 4 > 200 * 1024:
         raise Backend(f"router: width {width} + experts {n_experts} do not fit the kernel's shared memory")
+    pc, groups, keep = _choice_args(choice, n_experts)
     if w_gate is not None and w_gate.dtype != w_router.dtype:
         raise Backend("router: router and shared-gate weights must share a dtype")
     if logits is not None and logits.numel() < n * (n_experts + 1):
@@ -388,7 +407,7 @@ def router_topk(h, w_router, w_gate, topk_ids, topk_w, gate, top_k, norm_topk, s
         _ptr(h, FLOATS, "h"), _is_bf16(h), _ptr(w_router, FLOATS), _ptr(w_gate, FLOATS), _is_bf16(w_router),
         _ptr(topk_ids, torch.int32), _ptr(topk_w, torch.float32), _ptr(gate, torch.float32),
         _ptr(probs_out, torch.float32), _ptr(logits, torch.float32), n, width, n_experts, top_k,
-        (1 if norm_topk else 0) | (2 if sigmoid else 0), _ptr(status, torch.int32), _stream()), "router_topk")
+        (1 if norm_topk else 0) | (2 if sigmoid else 0), pc, groups, keep, _ptr(status, torch.int32), _stream()), "router_topk")
 
 
 ROUTE_SMALL_TOKENS = 64
@@ -396,12 +415,14 @@ ROUTE_SMALL_TOKENS = 64
 
 def route_small_fits(width: int, n_experts: int) -> bool:
     # the second kernel's shared memory: probabilities of eight tokens, counts and cursors, and the step's pairs
-    return width * 4 <= 48 * 1024 and (8 * n_experts) * 4 + (2 * n_experts + 1) * 4 + ROUTE_SMALL_TOKENS * 32 * 8 <= 48 * 1024
+    return width * 4 <= 48 * 1024 and (16 * n_experts) * 4 + (2 * n_experts + 1) * 4 + ROUTE_SMALL_TOKENS * 32 * 8 <= 48 * 1024
 
 
 def route_small(h, w_router, w_gate, logits, topk_ids, topk_w, gate, top_k, norm_topk, offsets, perm_token,
-                perm_weight, inverse, status, probs_out=None, distinct=None, tiles=None, sigmoid=False):
-    """Router and permutation for at most ROUTE_SMALL_TOKENS tokens: logits over many blocks, then one
+                perm_weight, inverse, status, probs_out=None, distinct=None, tiles=None, sigmoid=False, choice=None,
+                n_real=None):
+    """``choice``: as for router_topk.  ``n_real``: experts from this id on have no rows (their pairs get inverse -1).
+    Router and permutation for at most ROUTE_SMALL_TOKENS tokens: logits over many blocks, then one
     block for softmax, top-k and the permutation.  ``logits``: float32 scratch [N, E + 1].  ``distinct``:
     an int64 tensor of one element to which the number of experts with at least one token is added.
     ``tiles``: as for moe_permute (the row tiles of the grouped tensor-core products; one per expert with rows)."""
@@ -409,6 +430,7 @@ def route_small(h, w_router, w_gate, logits, topk_ids, topk_w, gate, top_k, norm
     n_experts = w_router.shape[0]
     if n > ROUTE_SMALL_TOKENS or top_k > 32 or not route_small_fits(width, n_experts):
         raise Backend("route_small: too many tokens or experts for this kernel")
+    pc, groups, keep = _choice_args(choice, n_experts)
     _check(_fn("core", "esp_route_small")(
         _ptr(h, FLOATS, "h"), _is_bf16(h), _ptr(w_router, FLOATS), _ptr(w_gate, FLOATS), _is_bf16(w_router),
         _ptr(logits, torch.float32), _ptr(topk_ids, torch.int32), _ptr(topk_w, torch.float32),
@@ -417,12 +439,13 @@ def route_small(h, w_router, w_gate, logits, topk_ids, topk_w, gate, top_k, norm
         _ptr(inverse, torch.int32), _ptr(status, torch.int32), _ptr(distinct, torch.int64),
         _ptr(tiles[0], torch.int32) if tiles else None, _ptr(tiles[1], torch.int32) if tiles else None,
         _ptr(tiles[2], torch.int32) if tiles else None, _ptr(tiles[3], torch.int32) if tiles else None,
-        tiles[0].shape[0] if tiles else 0, _stream()), "route_small")
+        tiles[0].shape[0] if tiles else 0, pc, groups, keep, int(n_real if n_real is not None else n_experts), _stream()),
+        "route_small")
 
 
 def moe_permute(topk_ids, topk_w, n_experts, offsets, perm_token, perm_weight, inverse, status, tiles=None,
-                distinct=None):
-    """``distinct``: as for route_small.  ``tiles``: optional (tile_group, tile_row0, tile_count, n_tiles) int32 tensors that receive the
+                distinct=None, n_ids=None):
+    """``n_ids``: ids from n_experts up to this name experts without rows (their pairs get inverse -1).  ``distinct``: as for route_small.  ``tiles``: optional (tile_group, tile_row0, tile_count, n_tiles) int32 tensors that receive the
     list of row tiles (of at most TC05_TILE_ROWS rows) for the grouped tensor-core products."""
     n, top_k = topk_ids.shape
     if (2 * n_experts + 1) * 4 > 48 * 1024:
@@ -433,29 +456,33 @@ def moe_permute(topk_ids, topk_w, n_experts, offsets, perm_token, perm_weight, i
         _ptr(tiles[0], torch.int32) if tiles else None, _ptr(tiles[1], torch.int32) if tiles else None,
         _ptr(tiles[2], torch.int32) if tiles else None, _ptr(tiles[3], torch.int32) if tiles else None,
         TC05_TILE_ROWS if tiles else 0, tiles[0].shape[0] if tiles else 0, _ptr(status, torch.int32),
-        _ptr(distinct, torch.int64), _stream()), "moe_permute")
+        _ptr(distinct, torch.int64), int(n_ids if n_ids is not None else n_experts), _stream()), "moe_permute")
 
 
-def moe_combine(expert_out, topk_ids, inverse, gate, shared, y):
+def moe_combine(expert_out, topk_ids, inverse, gate, shared, y, passing=None):
+    """``passing``: None, or (topk_w, ident float32 [tokens, width], n_real): a chosen id from n_real on adds its weight
+    times the token's row of ``ident`` instead of an expert's row."""
     n, width = y.shape
+    pw, pi, pn = (_ptr(passing[0], torch.float32), _ptr(passing[1], torch.float32, "ident"), int(passing[2])) if passing else (None, None, 0)
     _check(_fn("core", "esp_moe_combine")(
         _ptr(expert_out, torch.float32), _ptr(topk_ids, torch.int32), _ptr(inverse, torch.int32),
         _ptr(gate, torch.float32), _ptr(shared, torch.float32), _ptr(y, torch.float32), n, width, topk_ids.shape[1],
-        _stream()), "moe_combine")
+        pw, pi, pn, _stream()), "moe_combine")
 
 
 def moe_combine_add_rmsnorm(expert_out, topk_ids, inverse, gate, shared, x, gamma, h, eps, rows=None, write_x=True,
-                            h32=None):
+                            h32=None, passing=None):
     """moe_combine followed by add_rmsnorm in one kernel (same operations in the same order): x (+)= combined
-    expert outputs, h = rmsnorm(x) * gamma.  Width a multiple of 4, at most 16384."""
+    expert outputs, h = rmsnorm(x) * gamma.  Width a multiple of 4, at most 16384.  ``passing``: as for moe_combine."""
     n_rows, width = h.shape
+    pw, pi, pn = (_ptr(passing[0], torch.float32), _ptr(passing[1], torch.float32, "ident"), int(passing[2])) if passing else (None, None, 0)
     if width % 4 != 0 or width > 16384:
         raise Backend(f"moe_combine_add_rmsnorm: width {width} not taken")
     _check(_fn("core", "esp_moe_combine_add_rmsnorm")(
         _ptr(expert_out, torch.float32), _ptr(topk_ids, torch.int32), _ptr(inverse, torch.int32),
         _ptr(gate, torch.float32), _ptr(shared, torch.float32), _ptr(x, torch.float32), _ptr(gamma, torch.float32),
         _ptr(rows, torch.int32), _ptr(h, FLOATS, "h"), _is_bf16(h), _ptr(h32, torch.float32), n_rows, width,
-        topk_ids.shape[1], float(eps), 1 if write_x else 0, _stream()), "moe_combine_add_rmsnorm")
+        topk_ids.shape[1], float(eps), 1 if write_x else 0, pw, pi, pn, _stream()), "moe_combine_add_rmsnorm")
 
 
 def pick_tokens(logits, temperature, top_p, rng_state, row_slot, tokens):
@@ -831,8 +858,12 @@ def per_head_linear(a, lda, a_head, w, out, ldo, o_head, n_rows, heads, kin, nou
     if tuple(w.shape) != (heads, nout, kin) or kin * 8 * 4 > 48 * 1024:
         raise Backend(f"per_head_linear: weights {tuple(w.shape)} do not fit heads {heads}, {nout} x {kin}")
     code = {torch.float32: 0, torch.bfloat16: 1}
+    # ``a`` may be a view of the leading columns of wider rows (its row stride is lda)
+    if not a.is_cuda or a.dtype not in FLOATS or a.stride(-1) != 1 or (a.dim() == 2 and a.shape[0] > 1 and a.stride(0) != lda):
+        raise Backend("per_head_linear: a must be rows of unit column stride whose row stride is lda")
+    pa = a.data_ptr()
     _check(_fn("mixers", "esp_per_head_linear")(
-        _ptr(a, FLOATS, "a"), code[a.dtype], int(lda), int(a_head), _ptr(w, FLOATS, "w"), code[w.dtype],
+        pa, code[a.dtype], int(lda), int(a_head), _ptr(w, FLOATS, "w"), code[w.dtype],
         _ptr(out, FLOATS, "out"), code[out.dtype], int(ldo), int(o_head), int(n_rows), heads, kin, nout, _stream()),
         "per_head_linear")
 
@@ -1119,8 +1150,8 @@ def channel_decay_prepare(z, bias, tau, q, q_scale, q_out):
         _ptr(q_out, torch.float32, "q_out"), z.shape[0], z.shape[1], _stream()), "channel_decay_prepare")
 
 
-def causal_conv(x, w, conv_state, tok_seq, seq_start, seq_slot, y, n_seqs, taps, silu=True):
-    """y = act(causal convolution of x over ``taps`` positions per channel) within every sequence (w float32 [C, taps],
+def causal_conv(x, w, conv_state, tok_seq, seq_start, seq_slot, y, n_seqs, taps, silu=True, bias=None):
+    """y = act(causal convolution of x over ``taps`` positions per channel (+ bias float32 [C])) within every sequence (w float32 [C, taps],
     last column the token's own); conv_state float32 [slots, (taps - 1) * C] (a view with its slot stride) holds a
     sequence's last taps - 1 inputs and is brought up to date.  x float32 rows that may be parts of wider rows."""
     if taps > CONV_MAX_TAPS:
@@ -1130,7 +1161,65 @@ def causal_conv(x, w, conv_state, tok_seq, seq_start, seq_slot, y, n_seqs, taps,
     if tuple(y.shape) != tuple(x.shape) or tuple(w.shape) != (channels, taps):
         raise Backend("causal_conv: shapes disagree")
     _check(_fn("mixers", "esp_causal_conv")(
-        px, ldx, _ptr(w, torch.float32, "w"), conv_state.data_ptr() if conv_state is not None else None,
+        px, ldx, _ptr(w, torch.float32, "w"), _ptr(bias, torch.float32, "bias"),
+        conv_state.data_ptr() if conv_state is not None else None,
         conv_state.stride(0) if conv_state is not None else 0, _ptr(tok_seq, torch.int32), _ptr(seq_start, torch.int32),
         _ptr(seq_slot, torch.int32), _ptr(y, torch.float32, "y"), x.shape[0], int(n_seqs), channels, taps, 1 if silu else 0,
         _stream()), "causal_conv")
+
+
+# ---------------------------------------------------------------------------
+# selective scan, a scalar gate per head, neighbour-pair rotation with unit heads and blended values
+
+SELECTIVE_MAX_STATE = 512
+
+
+def selective_scan(x, dt_raw, bc, z, a_log, d_skip, state, seq_start, seq_slot, y, n_seqs, channels, n_state):
+    """The selective scan over the runs of rows that the sequences bring, from and to ``state`` (float32 [slots, >=
+    channels * n_state], a channel's entries side by side): dt = softplus(dt_raw); S <- exp(-dt exp(a_log)) S + dt x B;
+    y = (S . C + d_skip x) silu(z).  x, dt_raw, z: float32 [rows, channels] (may be parts of wider rows); bc: float32
+    [rows, 2 * n_state], B then C; y: [rows, channels] float32 or bfloat16.  All arithmetic 32-bit."""
+    if n_state > SELECTIVE_MAX_STATE:
+        raise Backend(f"selective_scan: {n_state} state entries a channel are beyond the {SELECTIVE_MAX_STATE} this kernel takes")
+    if state.dtype != torch.float32 or state.stride(1) != 1 or state.shape[1] < channels * n_state:
+        raise Backend("selective_scan: the state rows are too short or not float32")
+    if tuple(a_log.shape) != (channels, n_state) or bc.shape[1] != 2 * n_state or tuple(y.shape) != (x.shape[0], channels):
+        raise Backend("selective_scan: shapes disagree")
+    (px, ldx), (pdt, lddt), (pbc, ldbc), (pz, ldz) = (_rows_ld(t, n) for t, n in ((x, "x"), (dt_raw, "dt_raw"), (bc, "bc"), (z, "z")))
+    _check(_fn("mixers", "esp_selective_scan")(
+        px, ldx, pdt, lddt, pbc, ldbc, pz, ldz, _ptr(a_log, torch.float32, "a_log"), _ptr(d_skip, torch.float32, "d_skip"),
+        state.data_ptr(), state.stride(0), _ptr(seq_start, torch.int32), _ptr(seq_slot, torch.int32), _ptr(y, FLOATS, "y"),
+        _is_bf16(y), int(n_seqs), int(channels), int(n_state), _stream()), "selective_scan")
+
+
+def head_scalar_gate(o, gate, y, heads, value_dim):
+    """y[n, h, :] = o[n, h, :] * sigmoid(gate[n, h]); o float32 [rows, heads * value_dim], gate float32 [rows, heads]
+    (may be part of wider rows), y float32 or bfloat16."""
+    pg, ldg = _rows_ld(gate, "gate")
+    if tuple(y.shape) != tuple(o.shape) or o.shape[1] != heads * value_dim:
+        raise Backend("head_scalar_gate: shapes disagree")
+    _check(_fn("mixers", "esp_head_scalar_gate")(
+        _ptr(o, torch.float32, "o"), pg, ldg, _ptr(y, FLOATS, "y"), _is_bf16(y), o.shape[0], heads, value_dim, _stream()),
+        "head_scalar_gate")
+
+
+def pair_rope_unitnorm_kvwrite(qkv, bias, inv_freq, rot, eps, unit_norm, v_shared, blend_mode, blend, tok_seq, tok_pos, q_out,
+                               k_cache, v_cache, block_table, page, nh, nkv, hd, vd, write_kv, status):
+    """Bias, rotation of neighbouring channel pairs (2i with 2i + 1) of the first ``rot`` channels of every query and key
+    head by position * inv_freq[i], every head then divided by its root mean square (``unit_norm``), values copied to
+    (blend_mode 1) or blended with (blend_mode 2: (1 - blend) v + blend v_shared, ``blend`` a float32 tensor of one
+    element on the device) the float32 rows v_shared [rows, nkv * vd]; queries to q_out, keys and values to the paged
+    cache.  qkv float32 [rows, nh * hd + nkv * hd + nkv * vd]."""
+    if qkv.shape[1] != nh * hd + nkv * hd + nkv * vd:
+        raise Backend("pair_rope_unitnorm_kvwrite: the projection's width does not fit the head sizes")
+    if rot and (inv_freq is None or inv_freq.shape[0] < rot // 2):
+        raise Backend("pair_rope_unitnorm_kvwrite: too few frequencies")
+    if blend_mode and (v_shared is None or v_shared.numel() < qkv.shape[0] * nkv * vd):
+        raise Backend("pair_rope_unitnorm_kvwrite: the shared value rows are missing or too small")
+    _check(_fn("core", "esp_pair_rope_unitnorm_kvwrite")(
+        _ptr(qkv, torch.float32, "qkv"), _ptr(bias, torch.float32, "bias"), _ptr(inv_freq, torch.float32, "inv_freq"), int(rot),
+        float(eps), 1 if unit_norm else 0, _ptr(v_shared, torch.float32, "v_shared"), int(blend_mode),
+        _ptr(blend, torch.float32, "blend"), _ptr(tok_seq, torch.int32), _ptr(tok_pos, torch.int32), _ptr(q_out, FLOATS, "q_out"),
+        _ptr(k_cache, q_out.dtype, "k_cache"), _ptr(v_cache, q_out.dtype, "v_cache"), _is_bf16(q_out),
+        _ptr(block_table, torch.int32), block_table.shape[1], k_cache.shape[0], page, qkv.shape[0], nh, nkv, hd, vd,
+        1 if write_kv else 0, _ptr(status, torch.int32), _stream()), "pair_rope_unitnorm_kvwrite")

@@ -464,3 +464,124 @@ ESP_API int esp_widenorm_rope_kvwrite(const float* qkv, const float* q_w, const 
                        block_table, table_stride, n_pages, page, nh, nkv, hd, vd, write_kv, status);
     return esp_launch_status();
 }
+
+// ---------------------------------------------------------------- neighbour-pair rotation, unit root mean square per head,
+// values blended with those of an earlier layer
+// qkv: [n_tokens, nh*hd + nkv*hd + nkv*vd] float, bias (may be null) of the same width.  Of the first ``rot`` channels of
+// every query and key head, channel 2i is rotated with channel 2i + 1 by the angle position * inv_freq[i] (a 32-bit
+// product; sine and cosine in 32-bit); the other channels pass unchanged.  With ``unit_norm`` every head is then divided
+// by its root mean square over hd (eps inside the root; no weight).  Values: blend_mode 1 copies the row's values
+// (bias added, unrounded) to v_shared [n_tokens, nkv*vd]; blend_mode 2 replaces them by (1 - lambda) v + lambda v_shared
+// with lambda read from the device.  Queries go to q_out [n_tokens, nh, hd], keys [pages, nkv, PAGE, hd] and values
+// [pages, nkv, PAGE, vd] to the token's place in the paged cache.  One block per token, a warp a head.
+namespace {
+constexpr int PAIR_ROPE_MAX_HD = 256;
+template <typename T>
+__global__ void pair_rope_unitnorm_kvwrite_kernel(const float* __restrict__ qkv, const float* __restrict__ bias,
+                                                  const float* __restrict__ inv_freq, int rot, float eps, int unit_norm,
+                                                  float* __restrict__ v_shared, int blend_mode,
+                                                  const float* __restrict__ lambda, const int* __restrict__ tok_seq,
+                                                  const int* __restrict__ tok_pos, T* __restrict__ q_out,
+                                                  T* __restrict__ k_cache, T* __restrict__ v_cache,
+                                                  const int* __restrict__ block_table, int table_stride, int n_pages,
+                                                  int page, int nh, int nkv, int hd, int vd, int write_kv,
+                                                  int* __restrict__ status) {
+    pdl_trigger();
+    pdl_wait();
+    const int n = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+    const int pos = tok_pos[n], seq = tok_seq[n];
+    const size_t width = (size_t)(nh + nkv) * hd + (size_t)nkv * vd;
+    const float* src = qkv + (size_t)n * width;
+    int page_id = -1;
+    if (write_kv) {
+        page_id = block_table[(size_t)seq * table_stride + pos / page];
+        if (page_id < 0 || page_id >= n_pages) {
+            if (threadIdx.x == 0) atomicOr(status, ESP_STATUS_BAD_INDEX);
+            page_id = -1;
+        }
+    }
+    const int in_page = pos % page;
+    const float p = (float)pos;
+    constexpr int PER = PAIR_ROPE_MAX_HD / 64;             // pairs of channels a lane holds
+    for (int head = warp; head < nh + 2 * nkv; head += nwarp) {
+        if (head < nh + nkv) {
+            const float* x = src + (size_t)head * hd;
+            const float* b = bias ? bias + (size_t)head * hd : nullptr;
+            float lo[PER], hi[PER];
+            float ss = 0.f;
+#pragma unroll
+            for (int j = 0; j < PER; j++) {
+                const int c = 2 * (lane + 32 * j);
+                lo[j] = hi[j] = 0.f;
+                if (c >= hd) continue;
+                float u = x[c] + (b ? b[c] : 0.f);
+                float v = c + 1 < hd ? x[c + 1] + (b ? b[c + 1] : 0.f) : 0.f;
+                if (c + 1 < rot) {
+                    float sn, cs;
+                    sincosf(p * inv_freq[c >> 1], &sn, &cs);
+                    const float ru = u * cs - v * sn, rv = v * cs + u * sn;
+                    u = ru;
+                    v = rv;
+                }
+                lo[j] = u;
+                hi[j] = v;
+                ss = fmaf(u, u, ss);
+                ss = fmaf(v, v, ss);
+            }
+            ss = warp_sum(ss);
+            const float inv = unit_norm ? 1.0f / sqrtf(ss / (float)hd + eps) : 1.0f;
+            T* dst;
+            if (head < nh) dst = q_out + ((size_t)n * nh + head) * hd;
+            else if (page_id >= 0) dst = k_cache + (((size_t)page_id * nkv + (head - nh)) * page + in_page) * hd;
+            else continue;
+#pragma unroll
+            for (int j = 0; j < PER; j++) {
+                const int c = 2 * (lane + 32 * j);
+                if (c < hd) dst[c] = from_f32<T>(lo[j] * inv);
+                if (c + 1 < hd) dst[c + 1] = from_f32<T>(hi[j] * inv);
+            }
+        } else {
+            const int vh = head - nh - nkv;
+            const size_t off = (size_t)(nh + nkv) * hd + (size_t)vh * vd;
+            const float* x = src + off;
+            const float* b = bias ? bias + off : nullptr;
+            float* shared_row = v_shared ? v_shared + (size_t)n * nkv * vd + (size_t)vh * vd : nullptr;
+            const float lam = blend_mode == 2 ? lambda[0] : 0.f;
+            T* dst = page_id >= 0 ? v_cache + (((size_t)page_id * nkv + vh) * page + in_page) * vd : nullptr;
+            for (int i = lane; i < vd; i += 32) {
+                float v = x[i] + (b ? b[i] : 0.f);
+                if (blend_mode == 1) shared_row[i] = v;
+                else if (blend_mode == 2) v = (1.0f - lam) * v + lam * shared_row[i];
+                if (dst) dst[i] = from_f32<T>(v);
+            }
+        }
+    }
+}
+}  // namespace
+
+ESP_API int esp_pair_rope_unitnorm_kvwrite(const float* qkv, const float* bias, const float* inv_freq, int rot, float eps,
+                                           int unit_norm, float* v_shared, int blend_mode, const float* lambda,
+                                           const int* tok_seq, const int* tok_pos, void* q_out, void* k_cache, void* v_cache,
+                                           int is_bf16, const int* block_table, int table_stride, int n_pages, int page,
+                                           int n_tokens, int nh, int nkv, int hd, int vd, int write_kv, int* status,
+                                           cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (hd <= 0 || hd > PAIR_ROPE_MAX_HD || vd <= 0 || nkv <= 0 || nh <= 0 || page <= 0 || rot < 0 || rot > hd || rot % 2 != 0 ||
+        (rot > 0 && !inv_freq) || blend_mode < 0 || blend_mode > 2 || (blend_mode != 0 && !v_shared) ||
+        (blend_mode == 2 && !lambda))
+        return (int)cudaErrorInvalidValue;
+    const int heads = nh + 2 * nkv;
+    const int threads = heads >= 8 ? 256 : 32 * heads;
+    if (is_bf16)
+        esp_launch_pdl(ESP_PDL_SMALL, pair_rope_unitnorm_kvwrite_kernel<bf16>, dim3(n_tokens), dim3(threads), 0, stream, qkv, bias,
+                       inv_freq, rot, eps, unit_norm, v_shared, blend_mode, lambda, tok_seq, tok_pos, (bf16*)q_out,
+                       (bf16*)k_cache, (bf16*)v_cache, block_table, table_stride, n_pages, page, nh, nkv, hd, vd, write_kv,
+                       status);
+    else
+        esp_launch_pdl(ESP_PDL_SMALL, pair_rope_unitnorm_kvwrite_kernel<float>, dim3(n_tokens), dim3(threads), 0, stream, qkv, bias,
+                       inv_freq, rot, eps, unit_norm, v_shared, blend_mode, lambda, tok_seq, tok_pos, (float*)q_out,
+                       (float*)k_cache, (float*)v_cache, block_table, table_stride, n_pages, page, nh, nkv, hd, vd, write_kv,
+                       status);
+    return esp_launch_status();
+}

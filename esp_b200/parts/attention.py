@@ -447,6 +447,128 @@ class WideNormAttention(Part):
         return y
 
 
+class UnitNormAttention(Part):
+    """Causal softmax attention over the paged cache with unit heads (see ``UnitNormAttentionSpec``): one packed q/k/v
+    product; one kernel adds the biases, rotates neighbouring channel pairs of the first channels of every head,
+    divides every query and key head by its root mean square, blends the values with those that the first blending
+    layer made for the same tokens, and stores keys (rotated, normed) and values (blended) in the cache; the
+    attention kernels take the scores' scale as given, a window and a learned sink per head.  The first blending
+    layer leaves its values of the step's tokens (32-bit, unrounded) in a workspace buffer that the later ones read.
+    Query head i reads key/value head i // (num_heads / num_kv_heads)."""
+
+    graph_safe = True
+
+    def __init__(self, spec, rt):
+        self.spec, self.rt = spec, rt
+        s = spec
+        if s.key_dim > 256 or s.value_dim > 256:
+            raise Unsupported("dim", f"{s.key_dim} / {s.value_dim}; the attention kernels take head sizes up to 256")
+        if s.num_heads % s.num_kv_heads != 0:
+            raise Unsupported("kv_heads", f"{s.num_kv_heads} does not divide {s.num_heads} heads")
+        if s.value_blend not in (None, "first", "blend"):
+            raise Unsupported("v_mix", f"{s.value_blend!r}")
+        self.q_width = s.num_heads * s.key_dim
+        self.k_width = s.num_kv_heads * s.key_dim
+        self.v_width = s.num_kv_heads * s.value_dim
+        self.o_width = s.num_heads * s.value_dim
+        self.qkv_width = self.q_width + self.k_width + self.v_width
+        self.position = None
+        if s.position is not None:
+            if s.position.rotary_dim % 2 or s.position.rotary_dim > s.key_dim:
+                raise Unsupported("rot.dims", f"{s.position.rotary_dim}; an even number of channels of a head of {s.key_dim}")
+            key = ("position", s.position)            # layers with the same encoding share one part (and its frequencies)
+            if key not in rt.shared_parts:
+                rt.shared_parts[key] = build("position", s.position, rt)
+            self.position = rt.shared_parts[key]
+        self.w_qkv = self.b_qkv = self.w_o = self.sink = self.blend = None
+
+    def children(self):
+        return [self.position] if self.position is not None else []
+
+    def _n(self, which, bias=False):
+        n = self.spec.names
+        return self.spec.prefix + getattr(n, which) + (n.bias if bias else "")
+
+    def param_specs(self):
+        s = self.spec
+        specs = [ParamSpec(self._n("q"), (self.q_width, s.hidden), "matrix"),
+                 ParamSpec(self._n("k"), (self.k_width, s.hidden), "matrix"),
+                 ParamSpec(self._n("v"), (self.v_width, s.hidden), "matrix"),
+                 ParamSpec(self._n("o"), (s.hidden, self.o_width), "matrix")]
+        if s.qkv_bias:
+            specs += [ParamSpec(self._n("q", True), (self.q_width,), "bias"),
+                      ParamSpec(self._n("k", True), (self.k_width,), "bias"),
+                      ParamSpec(self._n("v", True), (self.v_width,), "bias")]
+        if s.learned_sink:
+            specs.append(ParamSpec(self._n("sink"), (s.num_heads,), "attention_sink", init=(0.0, 1.0)))
+        if s.value_blend is not None:
+            specs.append(ParamSpec(self._n("value_blend"), (), "value_blend", init=(0.5, 0.1)))
+        return specs
+
+    def allocate(self, stored, rt):
+        s, dev = self.spec, rt.device
+        names = [self._n("q"), self._n("k"), self._n("v")]
+        self.w_qkv = torch.empty((self.qkv_width, s.hidden), dtype=rt.matrix_dtype([stored[n] for n in names]), device=dev)
+        self.w_o = torch.empty((s.hidden, self.o_width), dtype=rt.matrix_dtype([stored[self._n("o")]]), device=dev)
+        a, b = self.q_width, self.q_width + self.k_width
+        views = {names[0]: self.w_qkv[:a], names[1]: self.w_qkv[a:b], names[2]: self.w_qkv[b:], self._n("o"): self.w_o}
+        if s.qkv_bias:
+            self.b_qkv = torch.empty(self.qkv_width, dtype=torch.float32, device=dev)
+            views.update({self._n("q", True): self.b_qkv[:a], self._n("k", True): self.b_qkv[a:b],
+                          self._n("v", True): self.b_qkv[b:]})
+        if s.learned_sink:
+            self.sink = torch.empty(s.num_heads, dtype=torch.float32, device=dev)
+            views[self._n("sink")] = self.sink
+        if s.value_blend is not None:
+            self.blend = torch.empty(1, dtype=torch.float32, device=dev)
+            views[self._n("value_blend")] = self.blend[0]
+        return views
+
+    def kv_layout(self):
+        s = self.spec
+        return KvLayout(s.num_kv_heads, s.key_dim, s.window, value_dim=s.value_dim if s.value_dim != s.key_dim else None)
+
+    def state_spec(self):
+        return None
+
+    # -- which kernel a step of n token rows gets, and the index lists it needs ----------
+    def kernel_for(self, n: int, page: int = PAGE) -> str:
+        s = self.spec
+        return scaled_kernel_for(self.rt, s.key_dim, s.value_dim, s.scale, n, page)
+
+    def step_arrays_key(self):
+        s = self.spec
+        return ("attention_unitnorm", self.rt.dtype, s.key_dim, s.value_dim, s.scale > 0)
+
+    def step_arrays(self, step):
+        return scaled_tiles(self.kernel_for(step.n_tokens), step)
+
+    def forward(self, h, ctx, layer):
+        s, rt = self.spec, self.rt
+        n = h.shape[0]
+        table = ctx.block_tables[layer.group]
+        qkv = rt.ws.get("attn_qkv", (n, self.qkv_width), torch.float32)
+        linear(rt, h, self.w_qkv, qkv)
+        q = rt.ws.get("attn_q", (n, self.q_width), rt.dtype)
+        pos = self.position
+        shared_v = None
+        if s.value_blend is not None:
+            # the first blending layer's values of this step's tokens, for every later one of the same width
+            shared_v = rt.ws.get(f"attn_first_values_{self.v_width}", (n, self.v_width), torch.float32)
+        ops.pair_rope_unitnorm_kvwrite(qkv, self.b_qkv, pos.inv_freq if pos is not None else None,
+                                       pos.spec.rotary_dim if pos is not None else 0, s.eps, s.unit_heads, shared_v,
+                                       {None: 0, "first": 1, "blend": 2}[s.value_blend], self.blend, ctx.tok_seq, ctx.tok_pos, q,
+                                       layer.k, layer.v, table, layer.page, s.num_heads, s.num_kv_heads, s.key_dim, s.value_dim,
+                                       layer.writes, rt.status)
+        o = rt.ws.get("attn_o", (n, self.o_width), rt.dtype)
+        scaled_attend(rt, self.kernel_for(n, layer.page), q, o, ctx, layer, s.num_heads, s.num_kv_heads, s.key_dim, s.value_dim,
+                      s.scale, self.sink if s.learned_sink else False, window=s.window)
+        y = rt.ws.get("mixer_out", (n, s.hidden), torch.float32)
+        linear(rt, o, self.w_o, y)
+        return y
+
+
 register("mixer", "attention", Attention)
 register("mixer", "attention_qknorm", NormedAttention)
 register("mixer", "attention_widenorm", WideNormAttention)
+register("mixer", "attention_unitnorm", UnitNormAttention)

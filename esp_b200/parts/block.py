@@ -26,18 +26,25 @@ class PreNormResidualBlock(Part):
         self.ffn = build("ffn", spec.ffn, rt)
 
     def children(self):
-        return [self.mixer_norm, self.mixer, self.ffn_norm, self.ffn]
+        return [p for p in (self.mixer_norm, self.mixer, self.ffn_norm, self.ffn) if p is not None]
 
     def forward(self, x, pending, ctx, layer):
         rt = self.rt
         h = rt.ws.get("block_h", tuple(x.shape), rt.dtype)
         self.mixer_norm.forward(x, plain_delta(self.mixer_norm, pending), h)
         delta = self.mixer.forward(h, ctx, layer)
-        h32 = None
-        if rt.dtype != torch.float32 and getattr(self.ffn, "wants_f32_input", False):
-            h32 = rt.ws.get("block_h32", tuple(x.shape), torch.float32)
-        self.ffn_norm.forward(x, plain_delta(self.ffn_norm, delta), h, h32=h32)
-        return self.ffn.forward(h, ctx, h32=h32)
+        if self.ffn is not None:                 # a layer may be a mixer alone
+            h32 = None
+            if rt.dtype != torch.float32 and getattr(self.ffn, "wants_f32_input", False):
+                h32 = rt.ws.get("block_h32", tuple(x.shape), torch.float32)
+            self.ffn_norm.forward(x, plain_delta(self.ffn_norm, delta), h, h32=h32)
+            delta = self.ffn.forward(h, ctx, h32=h32)
+        if "residual_trace" in ctx.aux:
+            # debugging aid (see ScaledDepthMixBlock._trace): the add is done here so that x is the layer's result
+            x.add_(plain_delta(None, delta))
+            ctx.aux["residual_trace"].append(x.clone())
+            return None
+        return delta
 
 
 class ScaledDepthMixBlock(Part):

@@ -15,18 +15,19 @@ class DeferredMoeCombine:
     the pieces of the combine.  A norm that knows the fused kernel adds and normalises in one launch
     (``fused_add_rmsnorm``); anything else calls ``materialize()`` and gets the plain tensor."""
 
-    def __init__(self, rt, expert_out, ids, inverse, gate, shared, width):
+    def __init__(self, rt, expert_out, ids, inverse, gate, shared, width, passing=None):
         self.rt, self.expert_out, self.ids, self.inverse, self.gate, self.shared = rt, expert_out, ids, inverse, gate, shared
         self.width = width
+        self.passing = passing      # (weights, the block's input rows in 32-bit, first id without weights) or None
 
     def materialize(self):
         y = self.rt.ws.get("ffn_out", (self.ids.shape[0], self.width), torch.float32)
-        ops.moe_combine(self.expert_out, self.ids, self.inverse, self.gate, self.shared, y)
+        ops.moe_combine(self.expert_out, self.ids, self.inverse, self.gate, self.shared, y, passing=self.passing)
         return y
 
     def fused_add_rmsnorm(self, x, gamma, h, eps, rows, write_x, h32):
         ops.moe_combine_add_rmsnorm(self.expert_out, self.ids, self.inverse, self.gate, self.shared, x, gamma, h, eps,
-                                    rows=rows, write_x=write_x, h32=h32)
+                                    rows=rows, write_x=write_x, h32=h32, passing=self.passing)
 
 
 # Steps with at least AHEAD_ROWS rows start the shared expert's first product on a second stream before the
@@ -173,13 +174,23 @@ class MoeSwiGluShared(Part):
     optional renormalisation), routed SwiGLU experts whose outputs are scaled
     by their routing weight and summed in ascending expert id, plus a shared
     SwiGLU expert scaled by sigmoid(h . w_shared_gate)
-    (crates/esp/src/infer/decoder/moe.rs:135-256)."""
+    (crates/esp/src/infer/decoder/moe.rs:135-256).  Options of the spec: router outputs without an expert behind
+    them (a chosen one returns the block's input times its weight), a correction per output that counts for the
+    choice only, a choice limited to the best groups of neighbouring outputs, no shared expert."""
 
     graph_safe = True
 
     def __init__(self, spec, rt):
         self.spec = spec
         self.rt = rt
+        self.n_outputs = spec.num_experts + spec.identity_experts      # what the router scores
+        if spec.groups > 1:
+            if spec.groups > 32 or self.n_outputs % spec.groups or not 1 <= spec.keep_groups <= spec.groups:
+                raise Unsupported("router.groups", f"{spec.groups} groups (keep {spec.keep_groups}) over {self.n_outputs} router "
+                                                   f"outputs; the groups are equal and at most 32")
+            if spec.keep_groups * (self.n_outputs // spec.groups) < spec.top_k:
+                raise Unsupported("router.groups", "the kept groups hold fewer experts than are chosen")
+        self.correction = None
         self.w_router = self.w_shared_gate = None
         self.w_gate_up = self.w_down = None            # [E, 2Im, H], [E, H, Im]
         self.w_shared_gate_up = self.w_shared_down = None
@@ -196,11 +207,14 @@ class MoeSwiGluShared(Part):
     def param_specs(self):
         s = self.spec
         router, shared_gate, shared, experts = self._names()
-        specs = [ParamSpec(router, (s.num_experts, s.hidden), "matrix"),
-                 ParamSpec(shared_gate, (1, s.hidden), "matrix"),
-                 ParamSpec(shared[0], (s.shared_intermediate, s.hidden), "matrix"),
-                 ParamSpec(shared[1], (s.shared_intermediate, s.hidden), "matrix"),
-                 ParamSpec(shared[2], (s.hidden, s.shared_intermediate), "matrix")]
+        specs = [ParamSpec(router, (self.n_outputs, s.hidden), "matrix")]
+        if s.shared_intermediate is not None:
+            specs += [ParamSpec(shared_gate, (1, s.hidden), "matrix"),
+                      ParamSpec(shared[0], (s.shared_intermediate, s.hidden), "matrix"),
+                      ParamSpec(shared[1], (s.shared_intermediate, s.hidden), "matrix"),
+                      ParamSpec(shared[2], (s.hidden, s.shared_intermediate), "matrix")]
+        if s.correction is not None:
+            specs.append(ParamSpec(s.prefix + s.correction, (self.n_outputs,), "router_correction", init=(0.0, 0.02)))
         for gate, up, down in experts:
             specs += [ParamSpec(gate, (s.expert_intermediate, s.hidden), "matrix"),
                       ParamSpec(up, (s.expert_intermediate, s.hidden), "matrix"),
@@ -212,18 +226,23 @@ class MoeSwiGluShared(Part):
         dev = rt.device
         E, Im, Is, H = s.num_experts, s.expert_intermediate, s.shared_intermediate, s.hidden
         router, shared_gate, shared, experts = self._names()
-        rdt = rt.matrix_dtype([stored[router], stored[shared_gate]])
-        self.w_router = torch.empty((E, H), dtype=rdt, device=dev)
-        self.w_shared_gate = torch.empty((1, H), dtype=rdt, device=dev)
+        has_shared = Is is not None
+        rdt = rt.matrix_dtype([stored[router]] + ([stored[shared_gate]] if has_shared else []))
+        self.w_router = torch.empty((self.n_outputs, H), dtype=rdt, device=dev)
         gu_dt = rt.matrix_dtype([stored[n] for g, u, _d in experts for n in (g, u)])
         self.w_gate_up = torch.empty((E, 2 * Im, H), dtype=gu_dt, device=dev)
         self.w_down = torch.empty((E, H, Im), dtype=rt.matrix_dtype([stored[d] for _g, _u, d in experts]), device=dev)
-        sdt = rt.matrix_dtype([stored[shared[0]], stored[shared[1]]])
-        self.w_shared_gate_up = torch.empty((2 * Is, H), dtype=sdt, device=dev)
-        self.w_shared_down = torch.empty((H, Is), dtype=rt.matrix_dtype([stored[shared[2]]]), device=dev)
-        views = {router: self.w_router, shared_gate: self.w_shared_gate,
-                 shared[0]: self.w_shared_gate_up[:Is], shared[1]: self.w_shared_gate_up[Is:],
-                 shared[2]: self.w_shared_down}
+        views = {router: self.w_router}
+        if has_shared:
+            self.w_shared_gate = torch.empty((1, H), dtype=rdt, device=dev)
+            sdt = rt.matrix_dtype([stored[shared[0]], stored[shared[1]]])
+            self.w_shared_gate_up = torch.empty((2 * Is, H), dtype=sdt, device=dev)
+            self.w_shared_down = torch.empty((H, Is), dtype=rt.matrix_dtype([stored[shared[2]]]), device=dev)
+            views.update({shared_gate: self.w_shared_gate, shared[0]: self.w_shared_gate_up[:Is],
+                          shared[1]: self.w_shared_gate_up[Is:], shared[2]: self.w_shared_down})
+        if s.correction is not None:
+            self.correction = torch.empty(self.n_outputs, dtype=torch.float32, device=dev)
+            views[s.prefix + s.correction] = self.correction
         for e, (gate, up, down) in enumerate(experts):
             views[gate] = self.w_gate_up[e, :Im]
             views[up] = self.w_gate_up[e, Im:]
@@ -248,21 +267,32 @@ class MoeSwiGluShared(Part):
     def _forward_rows(self, h, y, ctx, row0, router_in):
         s, rt = self.spec, self.rt
         n, k, E, Im, H = h.shape[0], s.top_k, s.num_experts, s.expert_intermediate, s.hidden
+        R = self.n_outputs                       # router outputs: experts with weights, then those without
+        has_shared = s.shared_intermediate is not None
+        choice = (self.correction, s.groups, s.keep_groups) if (self.correction is not None or s.groups > 1) else None
         ws = rt.ws
         ids = ws.get("moe_ids", (n, k), torch.int32)
         wts = ws.get("moe_w", (n, k), torch.float32)
-        gate = ws.get("moe_gate", (n,), torch.float32)
+        gate = ws.get("moe_gate", (n,), torch.float32) if has_shared else None
         probs = None
         if rt.record_routing:
-            probs = torch.empty((n, E), dtype=torch.float32, device=rt.device)
-        offsets = ws.get("moe_offsets", (E + 1,), torch.int32)
+            probs = torch.empty((n, R), dtype=torch.float32, device=rt.device)
+        offsets = ws.get("moe_offsets", (R + 1,), torch.int32)
+        passing = None
+        if R > E:
+            ident = router_in
+            if ident.dtype != torch.float32:     # a caller without unrounded rows: the rounded ones, widened
+                ident = ws.get("moe_ident", tuple(h.shape), torch.float32)
+                ident.copy_(router_in)
+            passing = (wts, ident, E)
+
         perm_token = ws.get("moe_perm_token", (n * k,), torch.int32)
         perm_weight = ws.get("moe_perm_weight", (n * k,), torch.float32)
         inverse = ws.get("moe_inverse", (n, k), torch.int32)
         tiles = None
-        shared = ws.get("moe_shared_out", (n, H), torch.float32)
-        beside = n <= SIDE_STREAM_ROWS and rt.side_stream is not None
-        ahead = not beside and n >= AHEAD_ROWS and rt.side_stream is not None and rt.dtype == torch.bfloat16
+        shared = ws.get("moe_shared_out", (n, H), torch.float32) if has_shared else None
+        beside = has_shared and n <= SIDE_STREAM_ROWS and rt.side_stream is not None
+        ahead = has_shared and not beside and n >= AHEAD_ROWS and rt.side_stream is not None and rt.dtype == torch.bfloat16
         if ahead:
             main = torch.cuda.current_stream()
             rt.side_stream.wait_stream(main)
@@ -277,23 +307,25 @@ class MoeSwiGluShared(Part):
             with torch.cuda.stream(rt.side_stream):
                 _swiglu_mlp(rt, h, self.w_shared_gate_up, self.w_shared_down, shared, "moe_shared")
         uses_tc05 = grouped_uses_tc05(h, self.w_gate_up, n * k, n) and Im % 8 == 0
+        if uses_tc05 and R > E:
+            perm_token.zero_()                   # the gather reads n * k rows; those behind the last expert's are never placed
         if uses_tc05:
             max_tiles = (n * k + ops.TC05_TILE_ROWS - 1) // ops.TC05_TILE_ROWS + E
             tiles = (ws.get("moe_tile_group", (max_tiles,), torch.int32),
                      ws.get("moe_tile_row0", (max_tiles,), torch.int32),
                      ws.get("moe_tile_count", (max_tiles,), torch.int32), ws.get("moe_n_tiles", (1,), torch.int32))
-        if n <= ops.ROUTE_SMALL_TOKENS and ops.route_small_fits(H, E):
+        if n <= ops.ROUTE_SMALL_TOKENS and ops.route_small_fits(H, R):
             # few tokens: router and permutation (and the tile list, when the tensor-core products follow) in two
             # short launches
-            logits = ws.get("moe_logits", (n, E + 1), torch.float32)
+            logits = ws.get("moe_logits", (n, R + 1), torch.float32)
             ops.route_small(router_in, self.w_router, self.w_shared_gate, logits, ids, wts, gate, k, s.norm_topk,
                             offsets, perm_token, perm_weight, inverse, rt.status, probs, distinct=self.expert_reads,
-                            tiles=tiles)
+                            tiles=tiles, choice=choice, n_real=E)
         else:
             ops.router_topk(router_in, self.w_router, self.w_shared_gate, ids, wts, gate, k, s.norm_topk, rt.status,
-                            probs, logits=ws.get("moe_logits", (n, E + 1), torch.float32))
+                            probs, logits=ws.get("moe_logits", (n, R + 1), torch.float32), choice=choice)
             ops.moe_permute(ids, wts, E, offsets, perm_token, perm_weight, inverse, rt.status, tiles=tiles,
-                            distinct=self.expert_reads)
+                            distinct=self.expert_reads, n_ids=R)
         if rt.record_routing:
             ctx.aux.setdefault("routing", []).append((s.prefix, row0, ids.clone(), wts.clone(), probs))
         if ahead:
@@ -303,11 +335,11 @@ class MoeSwiGluShared(Part):
             main.wait_stream(rt.side_stream)
         elif ahead:
             linear(rt, act_s, self.w_shared_down, shared)
-        else:
+        elif has_shared:
             _swiglu_mlp(rt, h, self.w_shared_gate_up, self.w_shared_down, shared, "moe_shared")
         if y is None:
-            return DeferredMoeCombine(rt, expert_out, ids, inverse, gate, shared, H)
-        ops.moe_combine(expert_out, ids, inverse, gate, shared, y)
+            return DeferredMoeCombine(rt, expert_out, ids, inverse, gate, shared, H, passing)
+        ops.moe_combine(expert_out, ids, inverse, gate, shared, y, passing=passing)
         return y
 
     def experts(self, h, offsets, perm_token, perm_weight, rows, max_rows, tiles=None):
@@ -333,6 +365,37 @@ def _relu2_mlp(rt, h, w_up, w_down, out, tag):
     relu2_linear(rt, h, w_up, act, tag)
     linear(rt, act, w_down, out)
     return out
+
+
+class DenseRelu2(Part):
+    """y = W_down relu(W_up h)^2, no biases."""
+
+    graph_safe = True
+
+    def __init__(self, spec, rt):
+        self.spec, self.rt = spec, rt
+        self.w_up = self.w_down = None
+
+    def param_specs(self):
+        s, p = self.spec, self.spec.prefix
+        return [ParamSpec(p + s.up, (s.intermediate, s.hidden), "matrix"),
+                ParamSpec(p + s.down, (s.hidden, s.intermediate), "matrix")]
+
+    def allocate(self, stored, rt):
+        s, p = self.spec, self.spec.prefix
+        self.w_up = torch.empty((s.intermediate, s.hidden), dtype=rt.matrix_dtype([stored[p + s.up]]), device=rt.device)
+        self.w_down = torch.empty((s.hidden, s.intermediate), dtype=rt.matrix_dtype([stored[p + s.down]]), device=rt.device)
+        return {p + s.up: self.w_up, p + s.down: self.w_down}
+
+    def forward(self, h, ctx, h32=None):
+        rt, s = self.rt, self.spec
+        n = h.shape[0]
+        y = rt.ws.get("ffn_out", (n, s.hidden), torch.float32)
+        step = rt.ffn_chunk_tokens
+        for a in range(0, n, step):
+            b = min(n, a + step)
+            _relu2_mlp(rt, h[a:b], self.w_up, self.w_down, y[a:b], "relu2")
+        return y
 
 
 class ScaledInputMoe(Part):
@@ -466,4 +529,5 @@ register("ffn", "swiglu", DenseSwiGlu)
 register("ffn", "glu_clamped", ClampedGlu)
 register("ffn", "moe_sigmoid_scaled_input", ScaledInputMoe)
 register("ffn", "xielu", DenseXielu)
+register("ffn", "relu2", DenseRelu2)
 register("ffn", "moe_swiglu_shared", MoeSwiGluShared)

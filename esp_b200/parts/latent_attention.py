@@ -7,6 +7,7 @@ import torch
 from ..cache import KvLayout
 from ..cache.book import PAGE
 from ..csrc import ops
+from ..errors import Unsupported
 from .base import ParamSpec, Part, build, register
 from .linear import linear
 
@@ -25,27 +26,39 @@ class LatentAttention(Part):
 
     def __init__(self, spec, rt):
         self.spec, self.rt = spec, rt
-        key = ("position", spec.position)
-        if key not in rt.shared_parts:
-            rt.shared_parts[key] = build("position", spec.position, rt)
-        self.position = rt.shared_parts[key]
+        self.position = None
+        if spec.position is not None:
+            key = ("position", spec.position)
+            if key not in rt.shared_parts:
+                rt.shared_parts[key] = build("position", spec.position, rt)
+            self.position = rt.shared_parts[key]
+        elif spec.rot_dim:
+            raise Unsupported("rot", "a rotated key part without a position encoding")
+        if spec.kv_rank > 512:
+            raise Unsupported("kv_rank", f"{spec.kv_rank}; the latent attention kernels take up to 512 value channels a row")
+        self.w_q = None                          # full-rank queries (q_rank None): [queries; head gates] x hidden
         self.row = spec.kv_rank + spec.rot_dim
         self.q_head = spec.nope_dim + spec.rot_dim
-        self.w_dq = self.dq_norm = self.w_uq = self.w_dkv = self.dkv_norm = self.w_uk = self.w_uv = self.w_o = None
+        self.w_dq = self.dq_norm = self.w_uq = self.w_dkv = self.dkv_norm = self.w_uk = self.w_uv = self.w_o = self.w_gate = None
         self.w_uk_t = None
 
     def children(self):
-        return [self.position]
+        return [self.position] if self.position is not None else []
 
     def _n(self, which):
         return self.spec.prefix + getattr(self.spec.names, which)
 
     def param_specs(self):
         s = self.spec
-        specs = [ParamSpec(self._n("q_down"), (s.q_rank, s.hidden), "matrix"),
-                 ParamSpec(self._n("q_norm"), (s.q_rank,), "norm_scale"),
-                 ParamSpec(self._n("q_up"), (s.num_heads * self.q_head, s.q_rank), "matrix"),
-                 ParamSpec(self._n("k_up"), (s.num_heads * s.nope_dim, s.kv_rank), "matrix"),
+        if s.q_rank is not None:
+            specs = [ParamSpec(self._n("q_down"), (s.q_rank, s.hidden), "matrix"),
+                     ParamSpec(self._n("q_norm"), (s.q_rank,), "norm_scale"),
+                     ParamSpec(self._n("q_up"), (s.num_heads * self.q_head, s.q_rank), "matrix")]
+        else:
+            specs = [ParamSpec(self._n("q"), (s.num_heads * self.q_head, s.hidden), "matrix")]
+        if s.head_gate:
+            specs.append(ParamSpec(self._n("head_gate"), (s.num_heads, s.hidden), "matrix"))
+        specs += [ParamSpec(self._n("k_up"), (s.num_heads * s.nope_dim, s.kv_rank), "matrix"),
                  ParamSpec(self._n("v_up"), (s.num_heads * s.value_dim, s.kv_rank), "matrix"),
                  ParamSpec(self._n("o"), (s.hidden, s.num_heads * s.value_dim), "matrix")]
         if s.own_kv:
@@ -56,14 +69,27 @@ class LatentAttention(Part):
     def allocate(self, stored, rt):
         s, dev = self.spec, rt.device
         mat = lambda which, *shape: torch.empty(shape, dtype=rt.matrix_dtype([stored[self._n(which)]]), device=dev)
-        self.w_dq = mat("q_down", s.q_rank, s.hidden)
-        self.w_uq = mat("q_up", s.num_heads * self.q_head, s.q_rank)
         self.w_uk = mat("k_up", s.num_heads * s.nope_dim, s.kv_rank)
         self.w_uv = mat("v_up", s.num_heads * s.value_dim, s.kv_rank)
         self.w_o = mat("o", s.hidden, s.num_heads * s.value_dim)
-        self.dq_norm = torch.empty(s.q_rank, dtype=torch.float32, device=dev)
-        views = {self._n("q_down"): self.w_dq, self._n("q_up"): self.w_uq, self._n("k_up"): self.w_uk,
-                 self._n("v_up"): self.w_uv, self._n("o"): self.w_o, self._n("q_norm"): self.dq_norm}
+        views = {self._n("k_up"): self.w_uk, self._n("v_up"): self.w_uv, self._n("o"): self.w_o}
+        qw = s.num_heads * self.q_head
+        if s.q_rank is not None:
+            self.w_dq = mat("q_down", s.q_rank, s.hidden)
+            self.w_uq = mat("q_up", qw, s.q_rank)
+            self.dq_norm = torch.empty(s.q_rank, dtype=torch.float32, device=dev)
+            views.update({self._n("q_down"): self.w_dq, self._n("q_up"): self.w_uq, self._n("q_norm"): self.dq_norm})
+            if s.head_gate:
+                self.w_gate = mat("head_gate", s.num_heads, s.hidden)
+                views[self._n("head_gate")] = self.w_gate
+        else:
+            # the queries and the heads' gates are one product of the layer's input
+            names = [self._n("q")] + ([self._n("head_gate")] if s.head_gate else [])
+            self.w_q = torch.empty((qw + (s.num_heads if s.head_gate else 0), s.hidden),
+                                   dtype=rt.matrix_dtype([stored[n] for n in names]), device=dev)
+            views[names[0]] = self.w_q[:qw]
+            if s.head_gate:
+                views[names[1]] = self.w_q[qw:]
         if s.own_kv:
             self.w_dkv = mat("kv_down", self.row, s.hidden)
             self.dkv_norm = torch.empty(s.kv_rank, dtype=torch.float32, device=dev)
@@ -134,27 +160,48 @@ class LatentAttention(Part):
         s, rt, pos = self.spec, self.rt, self.position
         n, H = h.shape[0], s.num_heads
         table = ctx.block_tables[layer.group]
-        dq = rt.ws.get("la_dq", (n, s.q_rank), torch.float32)
-        linear(rt, h, self.w_dq, dq)
-        cq = rt.ws.get("la_cq", (n, s.q_rank), rt.dtype)
-        ops.add_rmsnorm(dq, None, self.dq_norm, cq, s.eps, write_x=False)
-        q = rt.ws.get("la_q", (n, H * self.q_head), torch.float32)
-        linear(rt, cq, self.w_uq, q)
+        qw = H * self.q_head
+        gate = None                              # float32 [n, H] (a view with its row stride): one number per token and head
+        if s.q_rank is not None:
+            dq = rt.ws.get("la_dq", (n, s.q_rank), torch.float32)
+            linear(rt, h, self.w_dq, dq)
+            cq = rt.ws.get("la_cq", (n, s.q_rank), rt.dtype)
+            ops.add_rmsnorm(dq, None, self.dq_norm, cq, s.eps, write_x=False)
+            q = rt.ws.get("la_q", (n, qw), torch.float32)
+            linear(rt, cq, self.w_uq, q)
+            if s.head_gate:
+                gate = rt.ws.get("la_gate", (n, H), torch.float32)
+                linear(rt, h, self.w_gate, gate)
+        else:
+            qg = rt.ws.get("la_q", (n, self.w_q.shape[0]), torch.float32)
+            linear(rt, h, self.w_q, qg)
+            q = qg[:, :qw]
+            if s.head_gate:
+                gate = qg[:, qw:]
+        inv_freq = pos.inv_freq if pos is not None else None
+        magnitude = pos.magnitude if pos is not None else 1.0
+        rot_dims = pos.spec.rotary_dim if pos is not None else 0
         if layer.writes:
             d = rt.ws.get("la_dkv", (n, self.row), torch.float32)
             linear(rt, h, self.w_dkv, d)
-            ops.latent_kv_store(d, self.dkv_norm, pos.inv_freq, pos.magnitude, pos.spec.rotary_dim, ctx.tok_seq, ctx.tok_pos,
+            ops.latent_kv_store(d, self.dkv_norm, inv_freq, magnitude, rot_dims, ctx.tok_seq, ctx.tok_pos,
                                 table, layer.k, layer.page, s.kv_rank, s.rot_dim, s.eps, rt.status)
         qx = rt.ws.get("la_qx", (n, H * self.row), rt.dtype)
-        ops.latent_q_rotate(q, pos.inv_freq, pos.magnitude, pos.spec.rotary_dim, ctx.tok_pos, qx, H, s.nope_dim, s.rot_dim,
-                            s.kv_rank)
-        ops.per_head_linear(q, H * self.q_head, self.q_head, self.w_uk_t, qx, H * self.row, self.row, n, H, s.nope_dim,
+        if s.rot_dim:
+            ops.latent_q_rotate(q, inv_freq, magnitude, rot_dims, ctx.tok_pos, qx, H, s.nope_dim, s.rot_dim, s.kv_rank)
+        ops.per_head_linear(q, q.stride(0), self.q_head, self.w_uk_t, qx, H * self.row, self.row, n, H, s.nope_dim,
                             s.kv_rank)
         o_lat = rt.ws.get("la_olat", (n, H * s.kv_rank), rt.dtype)
         self.attend(qx, o_lat, ctx, layer, table)
         o = rt.ws.get("la_o", (n, H * s.value_dim), rt.dtype)
-        ops.per_head_linear(o_lat, H * s.kv_rank, s.kv_rank, self.w_uv.view(H, s.value_dim, s.kv_rank), o, H * s.value_dim,
-                            s.value_dim, n, H, s.kv_rank, s.value_dim)
+        if gate is None:
+            ops.per_head_linear(o_lat, H * s.kv_rank, s.kv_rank, self.w_uv.view(H, s.value_dim, s.kv_rank), o, H * s.value_dim,
+                                s.value_dim, n, H, s.kv_rank, s.value_dim)
+        else:
+            o32 = rt.ws.get("la_o32", (n, H * s.value_dim), torch.float32)
+            ops.per_head_linear(o_lat, H * s.kv_rank, s.kv_rank, self.w_uv.view(H, s.value_dim, s.kv_rank), o32, H * s.value_dim,
+                                s.value_dim, n, H, s.kv_rank, s.value_dim)
+            ops.head_scalar_gate(o32, gate, o, H, s.value_dim)
         y = rt.ws.get("mixer_out", (n, s.hidden), torch.float32)
         linear(rt, o, self.w_o, y)
         return y

@@ -55,6 +55,23 @@ class ScalarRmsNorm(RmsNorm):
             self.weight.copy_(self.weight[0].clone().expand(self.spec.width))
 
 
+class OffsetRmsNorm(RmsNorm):
+    """RMS norm whose stored weight lies around zero: h = x * rsqrt(mean(x^2) + eps) * (1 + w).  The one is added once
+    the weights are in (in 32-bit), so the kernels of the plain form run it."""
+
+    def __init__(self, spec, rt):
+        super().__init__(spec, rt)
+        self._offset_done = False
+
+    def param_specs(self):
+        return [ParamSpec(self.spec.weight, (self.spec.width,), "norm_offset", init=(0.0, 0.1))]
+
+    def finalize(self):
+        if self.weight is not None and not self._offset_done:
+            self._offset_done = True
+            self.weight.add_(1.0)
+
+
 class DeferredPostNorm:
     """A sublayer's result on its way into the residual stream through a norm of its own: x += norm(y).  The norm that
     reads x next does that add and its own normalisation in one launch (``fused_add_rmsnorm``); anything else gets the
@@ -79,3 +96,4 @@ class DeferredPostNorm:
 
 register("norm", "rmsnorm", RmsNorm)
 register("norm", "rmsnorm_scalar", ScalarRmsNorm)
+register("norm", "rmsnorm_offset", OffsetRmsNorm)

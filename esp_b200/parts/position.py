@@ -102,4 +102,5 @@ class RopeScaled(Part):
 
 register("position", "rope_split_half", RopeSplitHalf)
 register("position", "rope_split_half_scaled", RopeScaled)
+register("position", "rope_neighbour_pairs", RopeScaled)     # the same frequencies; which channels form a pair is the kernel's business
 register("position", "none", NoPosition)
