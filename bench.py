@@ -520,6 +520,26 @@ def migosun_config(width, ff, layers, vocab, window):
             "streams": 2, "layers": out, "ranks": ranks}
 
 
+# --design sebevik: the decoder with attention through a latent, windowed attention with unit heads and a learned sink,
+# the selective scan, and routed experts with a corrected, group-limited choice, beside the Qwen2 MoE decoder of the same
+# width, depth, heads, dense and expert sizes (the closest model this library has: windowed grouped attention, a softmax
+# router over gated experts and a gated shared expert).  Dense feed-forwards in the even layers, experts in the odd ones.
+def sebevik_config(width, ff, layers, vocab, window):
+    heads = width // 128
+    att = {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "v_mix": True,
+           "rot": {"dims": 64, "base": 10000.0}, "mask": {"size": window}}
+    pattern = [{"type": "latent_attention", "mixer": {"heads": heads, "dim": 128, "vdim": 128, "kv_rank": min(512, width // 4),
+                                                      "scale": 128 ** -0.5}},
+               {"type": "attention", "mixer": att},
+               {"type": "mamba1", "mixer": {"inner": 2 * width, "state": 16, "dt_rank": width // 16, "conv": 4}},
+               {"type": "attention", "mixer": att}]
+    moe = {"kind": "moe", "router": {"experts": VUMEDRA_EXPERTS, "top": VUMEDRA_TOP, "identity": 4, "groups": {"count": 4, "keep": 2}},
+           "expert": {"ff": ff // 4}, "shared": {"ff": ff // 2}}
+    out = [{"type": pattern[i % 4]["type"], "mixer": dict(pattern[i % 4]["mixer"]),
+            "mlp": dict(moe) if i % 2 else {"kind": "dense", "ff": ff}} for i in range(layers)]
+    return {"architecture": "Sebevik", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "layers": out}
+
+
 def measure_design(torch, raw, prefill_tokens, batches, context, steps, warmup, clocks):
     """Prefill of one prompt and decode steps of a model with random weights: tokens per second, and device time
     by kind of kernel for one eager prefill and one eager decode step (library products count with the kernel
@@ -576,8 +596,8 @@ def bench_design(torch, a, pk):
     sizes = {"w1024": (1024, 2816, 8), "w2048": (2048, 5632, 8), "w4096": (4096, 11008, 8)}
     picked = [s for s in a.design_sizes.split(",") if s]
     vocab, window = 32768, 4096
-    vumedra, migosun = a.design == "vumedra", a.design == "migosun"
-    beside = ("Qwen2 MoE decoder of equal width, depth, heads, dense and expert sizes" if vumedra else
+    vumedra, migosun, sebevik = a.design == "vumedra", a.design == "migosun", a.design == "sebevik"
+    beside = ("Qwen2 MoE decoder of equal width, depth, heads, dense and expert sizes" if vumedra or sebevik else
               "Zusepel decoder of equal width, depth and feed-forward width" if migosun else
               "dense Qwen2 decoder of equal width, depth and feed-forward width")
     result = {"design": a.design, "beside": beside, "dtype": "bf16",
@@ -591,10 +611,12 @@ def bench_design(torch, a, pk):
             mine, other = migosun_config(width, ff, layers, vocab, window), zusepel_config(width, ff, layers, vocab, window)
         elif vumedra:
             mine, other = vumedra_config(width, ff, layers, vocab), sparse_qwen2_config(width, ff, layers, vocab)
+        elif sebevik:
+            mine, other = sebevik_config(width, ff, layers, vocab, window), sparse_qwen2_config(width, ff, layers, vocab)
         else:
             mine, other = zusepel_config(width, ff, layers, vocab, window), dense_qwen2_config(width, ff, layers, vocab)
         entry[a.design] = measure_design(torch, mine, a.prefill_tokens, (1, 8), a.context, a.steps, a.warmup, clocks)
-        entry["zusepel" if migosun else "qwen2_moe" if vumedra else "qwen2_dense"] = measure_design(
+        entry["zusepel" if migosun else "qwen2_moe" if vumedra or sebevik else "qwen2_dense"] = measure_design(
             torch, other, a.prefill_tokens, (1, 8), a.context, a.steps, a.warmup, clocks)
         result["sizes"][name] = entry
     result["clocks"] = clocks.summary()
@@ -604,10 +626,10 @@ def bench_design(torch, a, pk):
 
 def main() -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--design", default=None, choices=["zusepel", "vumedra", "migosun"],
+    ap.add_argument("--design", default=None, choices=["zusepel", "vumedra", "migosun", "sebevik"],
                     help="instead of the default workload: prefill and decode of this design at a few layer sizes, beside "
                          "the closest other decoder of equal size (the dense Qwen2 for zusepel, the Qwen2 with routed "
-                         "experts for vumedra, zusepel for migosun)")
+                         "experts for vumedra and sebevik, zusepel for migosun)")
     ap.add_argument("--design-sizes", default="w1024,w2048", help="with --design: which of w1024, w2048, w4096")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=32)

@@ -15,7 +15,7 @@ from typing import Any, Optional
 
 @dataclass(frozen=True)
 class NormSpec:
-    kind: str            # registry key, e.g. "rmsnorm"; "rmsnorm_offset": the stored weight lies around zero, the scale is 1 + w
+    kind: str            # registry key, e.g. "rmsnorm"; "rmsnorm_offset": the tensor holds the scale minus one
     width: int
     eps: float
     weight: str          # tensor name of the scale vector

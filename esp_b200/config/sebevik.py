@@ -1,4 +1,4 @@
-"""Configuration of the Sebevik decoder: a pre-norm stack whose norms store their weights around zero; each layer has
+"""Configuration of the Sebevik decoder: a pre-norm stack whose norm weights are offsets from one; each layer has
 one of three token mixers (attention through a cached latent without positions and with a sigmoid gate per head;
 grouped attention with biases, neighbour-pair rotation, unit heads, a sliding window, a learned sink per head and values
 blended with the first such layer's; the selective scan behind a short convolution) and an optional feed-forward (dense

@@ -56,7 +56,7 @@ class ScalarRmsNorm(RmsNorm):
 
 
 class OffsetRmsNorm(RmsNorm):
-    """RMS norm whose stored weight lies around zero: h = x * rsqrt(mean(x^2) + eps) * (1 + w).  The one is added once
+    """RMS norm whose tensor holds the scale minus one: h = x * rsqrt(mean(x^2) + eps) * (1 + w).  The one is added once
     the weights are in (in 32-bit), so the kernels of the plain form run it."""
 
     def __init__(self, spec, rt):

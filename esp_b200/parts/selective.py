@@ -11,7 +11,7 @@ from ..cache import StateSpec
 from ..csrc import ops
 from ..errors import Unsupported
 from .base import ParamSpec, Part, register
-from .linear import linear
+from .linear import SKINNY_ROWS, linear
 
 
 class SelectiveScan(Part):
@@ -55,7 +55,7 @@ class SelectiveScan(Part):
         f32 = lambda *shape: torch.empty(shape, dtype=torch.float32, device=dev)
         self.w_in = mat("in_proj", 2 * s.inner, s.hidden)
         self.w_x = mat("x_proj", self.low_width, s.inner)
-        self.w_dt = mat("dt_proj", s.inner, s.dt_rank)
+        self.w_dt = f32(s.inner, s.dt_rank)          # widened exactly: the step size's projection is always 32-bit
         self.w_o = mat("o", s.hidden, s.inner)
         self.conv_w, self.conv_b, self.dt_b = f32(s.inner, s.taps), f32(s.inner), f32(s.inner)
         self.a_log, self.skip = f32(s.inner, s.state), f32(s.inner)
@@ -84,8 +84,13 @@ class SelectiveScan(Part):
         low = rt.ws.get("sel_low", (n, self.low_width), torch.float32)          # dt_low | B | C
         linear(rt, xa, self.w_x, low)
         dt_raw = rt.ws.get("sel_dt", (n, C), torch.float32)
-        # the step size enters the recurrence: its projection is a true 32-bit product, whatever the engine's dtype
-        ops.gemm_simt(low[:, :s.dt_rank], self.w_dt, dt_raw, bias=self.dt_b)
+        # the step size enters the recurrence: its projection is a true 32-bit product, whatever the engine's dtype.  The
+        # 32-bit engine keeps the kernel with the fixed order of sums for every step; the bfloat16 engine hands steps of
+        # many rows to the library's 32-bit product (no reduced-precision matrix mode), as it does with its other products.
+        if rt.dtype == torch.float32 or n <= SKINNY_ROWS or torch.backends.cuda.matmul.allow_tf32:
+            ops.gemm_simt(low[:, :s.dt_rank], self.w_dt, dt_raw, bias=self.dt_b)
+        else:
+            torch.addmm(self.dt_b, low[:, :s.dt_rank], self.w_dt.t(), out=dt_raw)
         y = rt.ws.get("sel_y", (n, C), rt.dtype)
         ops.selective_scan(x, dt_raw, low[:, s.dt_rank:], xz[:, C:], self.a_log, self.skip, layer.state, ctx.seq_start,
                            ctx.seq_slot, y, ctx.n_seqs, C, s.state)

@@ -34,7 +34,7 @@ def unit_rms(x, eps):
 
 
 def offset_norm(x, w, eps):
-    """RMS norm whose stored weight lies around zero."""
+    """RMS norm whose tensor w holds the scale minus one."""
     return unit_rms(x, eps) * (1 + w)
 
 

@@ -37,14 +37,14 @@ CASE_A = {
 
 # a width that is no multiple of 8; one head; a window of one position (the query alone, beside the sink); a window
 # longer than any test sequence; no window at all; no rotation at all; a convolution of one tap (no inputs kept) and one
-# of five; head size 128; one state entry; every router output chosen; one group (no limit); only identity experts
-# besides one expert; a single blending layer (nothing to blend with)
+# of five; head size 128; one state entry; every router output chosen in both sparse layers (no choice can flip under
+# rounding); one group (no limit); one expert with weights beside three outputs without; a single blending layer (nothing to blend with)
 CASE_B = {
     "architecture": "Sebevik", "vocab": 97, "width": 100, "norm": {"eps": 1e-6},
     "layers": [
         {"type": "attention", "mixer": {"heads": 1, "kv_heads": 1, "dim": 16, "vdim": 16, "scale": 0.4,
                                         "rot": {"dims": 8, "base": 100.0}, "mask": {"size": 1}},
-         "mlp": _moe(1, 2, 3, (1, 1), 36, 20)},
+         "mlp": _moe(1, 4, 3, (1, 1), 36, 20)},
         {"type": "mamba1", "mixer": {"inner": 52, "state": 1, "dt_rank": 1, "conv": 1}, "mlp": None},
         {"type": "latent_attention", "mixer": {"heads": 1, "dim": 72, "vdim": 8, "kv_rank": 20, "scale": 0.1},
          "mlp": _moe(3, 3, 0, None, 28, 12)},
