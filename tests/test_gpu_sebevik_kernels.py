@@ -238,7 +238,7 @@ def scan_want(x, dt_raw, bc, z, a_log, skip, runs, state0=None):
     return torch.stack(ys), torch.stack(finals)
 
 
-@pytest.mark.parametrize("C, N", [(40, 1), (96, 16), (33, 24), (128, 40), (20, 130), (260, 8)])
+@pytest.mark.parametrize("C, N", [(40, 1), (96, 16), (33, 24), (128, 40), (20, 130), (260, 8), (12, 300)])
 def test_selective_scan_over_unequal_runs_from_and_to_the_state(C, N):
     g = torch.Generator().manual_seed(C + N)
     runs = [37, 1, 70, 2]
