@@ -398,17 +398,32 @@ int pick_vr(int H, const void* qx, const void* pool, void* out, const int* tok_s
 #undef ESP_LA
 }
 // y[n, h, :] = o[n, h, :] * sigmoid(gate[n * ldg + h]): one number per token and head on the head's whole output.
-template <typename T>
+// VEC: head sizes of whole pieces of four channels on aligned buffers: a thread takes a piece.
+template <typename T, bool VEC>
 __global__ void head_scalar_gate_kernel(const float* __restrict__ o, const float* __restrict__ gate, long long ldg,
                                         T* __restrict__ y, long long total, int H, int V) {
     pdl_trigger();
     pdl_wait();
-    for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total; idx += (long long)gridDim.x * blockDim.x) {
+    const long long step = (long long)gridDim.x * blockDim.x;
+    if (VEC) {
+        const long long pieces = total / 4;
+        const int per_head = V / 4;
+        for (long long q = blockIdx.x * (long long)blockDim.x + threadIdx.x; q < pieces; q += step) {
+            const long long nh = q / per_head;
+            const long long n = nh / H;
+            const int h = (int)(nh - n * H);
+            const float s = 1.0f / (1.0f + expf(-gate[n * ldg + h]));
+            const float4 v = reinterpret_cast<const float4*>(o)[q];
+            Vec4<T>::store(y + 4 * q, v.x * s, v.y * s, v.z * s, v.w * s);
+        }
+        return;
+    }
+    for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total; idx += step) {
         const long long nh = idx / V;
         const long long n = nh / H;
         const int h = (int)(nh - n * H);
         const float g = gate[n * ldg + h];
-        y[idx] = from_f32<T>(o[idx] / (1.0f + expf(-g)));
+        y[idx] = from_f32<T>(o[idx] * (1.0f / (1.0f + expf(-g))));
     }
 }
 }  // namespace
@@ -492,12 +507,19 @@ ESP_API int esp_head_scalar_gate(const float* o, const float* gate, long long ld
     if (n_rows <= 0) return 0;
     if (H <= 0 || V <= 0) return (int)cudaErrorInvalidValue;
     const long long total = (long long)n_rows * H * V;
-    const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
-    if (y_is_bf16)
-        esp_launch_pdl(ESP_PDL_SMALL, head_scalar_gate_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, o, gate, ldg, (bf16*)y,
-                       total, H, V);
-    else
-        esp_launch_pdl(ESP_PDL_SMALL, head_scalar_gate_kernel<float>, dim3(blocks), dim3(256), 0, stream, o, gate, ldg, (float*)y,
-                       total, H, V);
+    const bool vec = V % 4 == 0 && (((size_t)o | (size_t)y) & 15) == 0;      // from sizes and alignment alone
+    const long long items = vec ? total / 4 : total;
+    const int blocks = (int)((items + 255) / 256 < 148 * 16 ? (items + 255) / 256 : 148 * 16);
+#define ESP_HEAD_GATE(T, VEC)                                                                                        \
+    esp_launch_pdl(ESP_PDL_SMALL, head_scalar_gate_kernel<T, VEC>, dim3(blocks), dim3(256), 0, stream, o, gate, ldg, (T*)y, \
+                   total, H, V)
+    if (y_is_bf16) {
+        if (vec) ESP_HEAD_GATE(bf16, true);
+        else ESP_HEAD_GATE(bf16, false);
+    } else {
+        if (vec) ESP_HEAD_GATE(float, true);
+        else ESP_HEAD_GATE(float, false);
+    }
+#undef ESP_HEAD_GATE
     return esp_launch_status();
 }

@@ -476,7 +476,15 @@ ESP_API int esp_widenorm_rope_kvwrite(const float* qkv, const float* q_w, const 
 // [pages, nkv, PAGE, vd] to the token's place in the paged cache.  One block per token, a warp a head.
 namespace {
 constexpr int PAIR_ROPE_MAX_HD = 256;
-template <typename T>
+
+__device__ __forceinline__ void store_pair(float* dst, float a, float b) { *reinterpret_cast<float2*>(dst) = make_float2(a, b); }
+__device__ __forceinline__ void store_pair(bf16* dst, float a, float b) {
+    *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(a, b);
+}
+
+// PAIRS: head sizes are even and every row starts on an 8-byte boundary, so a lane loads a channel pair as one piece
+// and stores it as one; else channel by channel.  Which form runs depends on the sizes and the buffers' alignment alone.
+template <typename T, bool PAIRS>
 __global__ void pair_rope_unitnorm_kvwrite_kernel(const float* __restrict__ qkv, const float* __restrict__ bias,
                                                   const float* __restrict__ inv_freq, int rot, float eps, int unit_norm,
                                                   float* __restrict__ v_shared, int blend_mode,
@@ -488,6 +496,7 @@ __global__ void pair_rope_unitnorm_kvwrite_kernel(const float* __restrict__ qkv,
                                                   int* __restrict__ status) {
     pdl_trigger();
     pdl_wait();
+    extern __shared__ float rope_cs[];                    // [rot / 2] cosines, then [rot / 2] sines of this row's angles
     const int n = blockIdx.x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
     const int pos = tok_pos[n], seq = tok_seq[n];
@@ -503,6 +512,10 @@ __global__ void pair_rope_unitnorm_kvwrite_kernel(const float* __restrict__ qkv,
     }
     const int in_page = pos % page;
     const float p = (float)pos;
+    const int half = rot / 2;
+    // the row's angles are the same for every head: their cosines and sines are made once
+    for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf(p * inv_freq[i], &rope_cs[half + i], &rope_cs[i]);
+    __syncthreads();
     constexpr int PER = PAIR_ROPE_MAX_HD / 64;             // pairs of channels a lane holds
     for (int head = warp; head < nh + 2 * nkv; head += nwarp) {
         if (head < nh + nkv) {
@@ -515,11 +528,22 @@ __global__ void pair_rope_unitnorm_kvwrite_kernel(const float* __restrict__ qkv,
                 const int c = 2 * (lane + 32 * j);
                 lo[j] = hi[j] = 0.f;
                 if (c >= hd) continue;
-                float u = x[c] + (b ? b[c] : 0.f);
-                float v = c + 1 < hd ? x[c + 1] + (b ? b[c + 1] : 0.f) : 0.f;
+                float u, v;
+                if (PAIRS) {
+                    const float2 xv = *reinterpret_cast<const float2*>(x + c);
+                    u = xv.x;
+                    v = xv.y;
+                    if (b) {
+                        const float2 bv = *reinterpret_cast<const float2*>(b + c);
+                        u += bv.x;
+                        v += bv.y;
+                    }
+                } else {
+                    u = x[c] + (b ? b[c] : 0.f);
+                    v = c + 1 < hd ? x[c + 1] + (b ? b[c + 1] : 0.f) : 0.f;
+                }
                 if (c + 1 < rot) {
-                    float sn, cs;
-                    sincosf(p * inv_freq[c >> 1], &sn, &cs);
+                    const float cs = rope_cs[c >> 1], sn = rope_cs[half + (c >> 1)];
                     const float ru = u * cs - v * sn, rv = v * cs + u * sn;
                     u = ru;
                     v = rv;
@@ -538,8 +562,12 @@ __global__ void pair_rope_unitnorm_kvwrite_kernel(const float* __restrict__ qkv,
 #pragma unroll
             for (int j = 0; j < PER; j++) {
                 const int c = 2 * (lane + 32 * j);
-                if (c < hd) dst[c] = from_f32<T>(lo[j] * inv);
-                if (c + 1 < hd) dst[c + 1] = from_f32<T>(hi[j] * inv);
+                if (PAIRS) {
+                    if (c < hd) store_pair(dst + c, lo[j] * inv, hi[j] * inv);
+                } else {
+                    if (c < hd) dst[c] = from_f32<T>(lo[j] * inv);
+                    if (c + 1 < hd) dst[c + 1] = from_f32<T>(hi[j] * inv);
+                }
             }
         } else {
             const int vh = head - nh - nkv;
@@ -549,11 +577,30 @@ __global__ void pair_rope_unitnorm_kvwrite_kernel(const float* __restrict__ qkv,
             float* shared_row = v_shared ? v_shared + (size_t)n * nkv * vd + (size_t)vh * vd : nullptr;
             const float lam = blend_mode == 2 ? lambda[0] : 0.f;
             T* dst = page_id >= 0 ? v_cache + (((size_t)page_id * nkv + vh) * page + in_page) * vd : nullptr;
-            for (int i = lane; i < vd; i += 32) {
-                float v = x[i] + (b ? b[i] : 0.f);
-                if (blend_mode == 1) shared_row[i] = v;
-                else if (blend_mode == 2) v = (1.0f - lam) * v + lam * shared_row[i];
-                if (dst) dst[i] = from_f32<T>(v);
+            if (PAIRS) {
+                for (int i = 2 * lane; i < vd; i += 64) {
+                    float2 v = *reinterpret_cast<const float2*>(x + i);
+                    if (b) {
+                        const float2 bv = *reinterpret_cast<const float2*>(b + i);
+                        v.x += bv.x;
+                        v.y += bv.y;
+                    }
+                    if (blend_mode == 1) {
+                        *reinterpret_cast<float2*>(shared_row + i) = v;
+                    } else if (blend_mode == 2) {
+                        const float2 f = *reinterpret_cast<const float2*>(shared_row + i);
+                        v.x = (1.0f - lam) * v.x + lam * f.x;
+                        v.y = (1.0f - lam) * v.y + lam * f.y;
+                    }
+                    if (dst) store_pair(dst + i, v.x, v.y);
+                }
+            } else {
+                for (int i = lane; i < vd; i += 32) {
+                    float v = x[i] + (b ? b[i] : 0.f);
+                    if (blend_mode == 1) shared_row[i] = v;
+                    else if (blend_mode == 2) v = (1.0f - lam) * v + lam * shared_row[i];
+                    if (dst) dst[i] = from_f32<T>(v);
+                }
             }
         }
     }
@@ -573,15 +620,20 @@ ESP_API int esp_pair_rope_unitnorm_kvwrite(const float* qkv, const float* bias, 
         return (int)cudaErrorInvalidValue;
     const int heads = nh + 2 * nkv;
     const int threads = heads >= 8 ? 256 : 32 * heads;
-    if (is_bf16)
-        esp_launch_pdl(ESP_PDL_SMALL, pair_rope_unitnorm_kvwrite_kernel<bf16>, dim3(n_tokens), dim3(threads), 0, stream, qkv, bias,
-                       inv_freq, rot, eps, unit_norm, v_shared, blend_mode, lambda, tok_seq, tok_pos, (bf16*)q_out,
-                       (bf16*)k_cache, (bf16*)v_cache, block_table, table_stride, n_pages, page, nh, nkv, hd, vd, write_kv,
-                       status);
-    else
-        esp_launch_pdl(ESP_PDL_SMALL, pair_rope_unitnorm_kvwrite_kernel<float>, dim3(n_tokens), dim3(threads), 0, stream, qkv, bias,
-                       inv_freq, rot, eps, unit_norm, v_shared, blend_mode, lambda, tok_seq, tok_pos, (float*)q_out,
-                       (float*)k_cache, (float*)v_cache, block_table, table_stride, n_pages, page, nh, nkv, hd, vd, write_kv,
-                       status);
+    const size_t smem = (size_t)rot * sizeof(float);
+    const size_t ptrs = (size_t)qkv | (size_t)bias | (size_t)v_shared | (size_t)q_out | (size_t)k_cache | (size_t)v_cache;
+    const bool pairs = hd % 2 == 0 && vd % 2 == 0 && (ptrs & 7) == 0;
+#define ESP_PAIR_ROPE(T, PAIRS)                                                                                              \
+    esp_launch_pdl(ESP_PDL_SMALL, pair_rope_unitnorm_kvwrite_kernel<T, PAIRS>, dim3(n_tokens), dim3(threads), smem, stream, qkv,  \
+                   bias, inv_freq, rot, eps, unit_norm, v_shared, blend_mode, lambda, tok_seq, tok_pos, (T*)q_out, (T*)k_cache,    \
+                   (T*)v_cache, block_table, table_stride, n_pages, page, nh, nkv, hd, vd, write_kv, status)
+    if (is_bf16) {
+        if (pairs) ESP_PAIR_ROPE(bf16, true);
+        else ESP_PAIR_ROPE(bf16, false);
+    } else {
+        if (pairs) ESP_PAIR_ROPE(float, true);
+        else ESP_PAIR_ROPE(float, false);
+    }
+#undef ESP_PAIR_ROPE
     return esp_launch_status();
 }
