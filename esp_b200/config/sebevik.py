@@ -198,9 +198,9 @@ class SebevikConfig:
         return ModelPlan(architecture=ARCHITECTURE, hidden=self.width, vocab=self.vocab, max_positions=POSITION_BOUND,
                          blocks=blocks, schedule=schedule, final_norm=norm("final.norm"), embed_weight="embed",
                          head_weight=None,
-                         # a layer without feed-forward has no second norm; a checkpoint that stores one all the same
-                         # is read without it
-                         tolerated_suffixes=(".norm2",))
+                         # a layer without feed-forward has no second norm and an attention layer that blends nothing
+                         # has no blend weight; a checkpoint that stores them all the same is read without them
+                         tolerated_suffixes=(".norm2", ".mix.vmix"))
 
 
 register_architecture(ARCHITECTURE, MODEL_TYPE, SebevikConfig)
