@@ -399,8 +399,14 @@ int pick_vr(int H, const void* qx, const void* pool, void* out, const int* tok_s
 }
 // y[n, h, :] = o[n, h, :] * sigmoid(gate[n * ldg + h]): one number per token and head on the head's whole output.
 // VEC: head sizes of whole pieces of four channels on aligned buffers: a thread takes a piece.
-template <typename T, bool VEC>
-__global__ void head_scalar_gate_kernel(const float* __restrict__ o, const float* __restrict__ gate, long long ldg,
+__device__ __forceinline__ float4 gate_load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 gate_load4(const bf16* p) {
+    const uint2 v = *reinterpret_cast<const uint2*>(p);
+    return make_float4(__uint_as_float(v.x << 16), __uint_as_float(v.x & 0xffff0000u), __uint_as_float(v.y << 16),
+                       __uint_as_float(v.y & 0xffff0000u));
+}
+template <typename TI, typename T, bool VEC>
+__global__ void head_scalar_gate_kernel(const TI* __restrict__ o, const float* __restrict__ gate, long long ldg,
                                         T* __restrict__ y, long long total, int H, int V) {
     pdl_trigger();
     pdl_wait();
@@ -413,7 +419,7 @@ __global__ void head_scalar_gate_kernel(const float* __restrict__ o, const float
             const long long n = nh / H;
             const int h = (int)(nh - n * H);
             const float s = 1.0f / (1.0f + expf(-gate[n * ldg + h]));
-            const float4 v = reinterpret_cast<const float4*>(o)[q];
+            const float4 v = gate_load4(o + 4 * q);
             Vec4<T>::store(y + 4 * q, v.x * s, v.y * s, v.z * s, v.w * s);
         }
         return;
@@ -423,7 +429,39 @@ __global__ void head_scalar_gate_kernel(const float* __restrict__ o, const float
         const long long n = nh / H;
         const int h = (int)(nh - n * H);
         const float g = gate[n * ldg + h];
-        y[idx] = from_f32<T>(o[idx] * (1.0f / (1.0f + expf(-g))));
+        y[idx] = from_f32<T>(to_f32(o[idx]) * (1.0f / (1.0f + expf(-g))));
+    }
+}
+
+// Keys and values of every head of the step's tokens, made from their latents, into pages of their own: k float
+// [rows, H * K] and v float [rows, H * V] (with their row strides) go to k_pool [pages, H, page, K] and v_pool
+// [pages, H, page, V] at the token's place, the page of position p of sequence s being table[s * stride + p / page].
+// K and V are multiples of four.  One block a token.
+template <typename T>
+__global__ void heads_to_pages_kernel(const float* __restrict__ k, long long ldk, const float* __restrict__ v, long long ldv,
+                                      const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
+                                      const int* __restrict__ table, int table_stride, int n_pages, int page,
+                                      T* __restrict__ k_pool, T* __restrict__ v_pool, int H, int K, int V,
+                                      int* __restrict__ status) {
+    pdl_trigger();
+    pdl_wait();
+    const int n = blockIdx.x;
+    const int seq = tok_seq[n], pos = tok_pos[n];
+    const int pg = table[(size_t)seq * table_stride + pos / page];
+    if (pg < 0 || pg >= n_pages) {
+        if (threadIdx.x == 0) atomicOr(status, ESP_STATUS_BAD_INDEX);
+        return;
+    }
+    const int in_page = pos % page;
+    for (int e = threadIdx.x * 4; e < H * K; e += blockDim.x * 4) {
+        const int head = e / K, c = e - head * K;
+        const float4 x = *reinterpret_cast<const float4*>(k + (size_t)n * ldk + e);
+        Vec4<T>::store(k_pool + (((size_t)pg * H + head) * page + in_page) * K + c, x.x, x.y, x.z, x.w);
+    }
+    for (int e = threadIdx.x * 4; e < H * V; e += blockDim.x * 4) {
+        const int head = e / V, c = e - head * V;
+        const float4 x = *reinterpret_cast<const float4*>(v + (size_t)n * ldv + e);
+        Vec4<T>::store(v_pool + (((size_t)pg * H + head) * page + in_page) * V + c, x.x, x.y, x.z, x.w);
     }
 }
 }  // namespace
@@ -502,24 +540,43 @@ ESP_API int esp_attn_latent(const void* qx, const void* pool, void* out, int is_
                           window, scale, status, stream);
 }
 
-ESP_API int esp_head_scalar_gate(const float* o, const float* gate, long long ldg, void* y, int y_is_bf16, int n_rows, int H,
-                                 int V, cudaStream_t stream) {
+ESP_API int esp_head_scalar_gate(const void* o, int o_is_bf16, const float* gate, long long ldg, void* y, int y_is_bf16,
+                                 int n_rows, int H, int V, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     if (H <= 0 || V <= 0) return (int)cudaErrorInvalidValue;
     const long long total = (long long)n_rows * H * V;
     const bool vec = V % 4 == 0 && (((size_t)o | (size_t)y) & 15) == 0;      // from sizes and alignment alone
     const long long items = vec ? total / 4 : total;
     const int blocks = (int)((items + 255) / 256 < 148 * 16 ? (items + 255) / 256 : 148 * 16);
-#define ESP_HEAD_GATE(T, VEC)                                                                                        \
-    esp_launch_pdl(ESP_PDL_SMALL, head_scalar_gate_kernel<T, VEC>, dim3(blocks), dim3(256), 0, stream, o, gate, ldg, (T*)y, \
-                   total, H, V)
-    if (y_is_bf16) {
-        if (vec) ESP_HEAD_GATE(bf16, true);
-        else ESP_HEAD_GATE(bf16, false);
-    } else {
-        if (vec) ESP_HEAD_GATE(float, true);
-        else ESP_HEAD_GATE(float, false);
-    }
+#define ESP_HEAD_GATE(TI, T, VEC)                                                                                         \
+    esp_launch_pdl(ESP_PDL_SMALL, head_scalar_gate_kernel<TI, T, VEC>, dim3(blocks), dim3(256), 0, stream, (const TI*)o, gate, \
+                   ldg, (T*)y, total, H, V)
+#define ESP_HEAD_GATE_T(TI, T)                                                                                            \
+    do {                                                                                                                  \
+        if (vec) ESP_HEAD_GATE(TI, T, true);                                                                              \
+        else ESP_HEAD_GATE(TI, T, false);                                                                                 \
+    } while (0)
+    if (o_is_bf16 && y_is_bf16) ESP_HEAD_GATE_T(bf16, bf16);
+    else if (o_is_bf16) ESP_HEAD_GATE_T(bf16, float);
+    else if (y_is_bf16) ESP_HEAD_GATE_T(float, bf16);
+    else ESP_HEAD_GATE_T(float, float);
+#undef ESP_HEAD_GATE_T
 #undef ESP_HEAD_GATE
+    return esp_launch_status();
+}
+
+ESP_API int esp_heads_to_pages(const float* k, long long ldk, const float* v, long long ldv, const int* tok_seq,
+                               const int* tok_pos, const int* table, int table_stride, int n_pages, int page, void* k_pool,
+                               void* v_pool, int is_bf16, int n_rows, int H, int K, int V, int* status, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    if (H <= 0 || K <= 0 || V <= 0 || K % 4 != 0 || V % 4 != 0 || ldk % 4 != 0 || ldv % 4 != 0 || page <= 0 ||
+        (((size_t)k | (size_t)v | (size_t)k_pool | (size_t)v_pool) & 15) != 0)
+        return (int)cudaErrorInvalidValue;
+    if (is_bf16)
+        esp_launch_pdl(ESP_PDL_SMALL, heads_to_pages_kernel<bf16>, dim3(n_rows), dim3(256), 0, stream, k, ldk, v, ldv, tok_seq,
+                       tok_pos, table, table_stride, n_pages, page, (bf16*)k_pool, (bf16*)v_pool, H, K, V, status);
+    else
+        esp_launch_pdl(ESP_PDL_SMALL, heads_to_pages_kernel<float>, dim3(n_rows), dim3(256), 0, stream, k, ldk, v, ldv, tok_seq,
+                       tok_pos, table, table_stride, n_pages, page, (float*)k_pool, (float*)v_pool, H, K, V, status);
     return esp_launch_status();
 }

@@ -70,7 +70,8 @@ _SIGNATURES = {
     "esp_channel_decay_prepare": [P, P, c_float, P, c_longlong, c_float, P, c_longlong, c_int, P],
     "esp_selective_scan": [P, c_longlong, P, c_longlong, P, c_longlong, P, c_longlong, P, P, P, c_longlong, P, P, P, c_int, c_int,
                            c_int, c_int, P],
-    "esp_head_scalar_gate": [P, P, c_longlong, P, c_int, c_int, c_int, c_int, P],
+    "esp_head_scalar_gate": [P, c_int, P, c_longlong, P, c_int, c_int, c_int, c_int, P],
+    "esp_heads_to_pages": [P, c_longlong, P, c_longlong, P, P, P, c_int, c_int, c_int, P, P, c_int, c_int, c_int, c_int, c_int, P, P],
     "esp_pair_rope_unitnorm_kvwrite": [P, P, P, c_int, c_float, c_int, P, c_int, P, P, P, P, P, P, c_int, P, c_int, c_int, c_int,
                                        c_int, c_int, c_int, c_int, c_int, c_int, P, P],
     "esp_causal_conv": [P, c_longlong, P, P, P, c_longlong, P, P, P, P, c_int, c_int, c_int, c_int, c_int, P],
@@ -1193,14 +1194,27 @@ def selective_scan(x, dt_raw, bc, z, a_log, d_skip, state, seq_start, seq_slot, 
 
 
 def head_scalar_gate(o, gate, y, heads, value_dim):
-    """y[n, h, :] = o[n, h, :] * sigmoid(gate[n, h]); o float32 [rows, heads * value_dim], gate float32 [rows, heads]
-    (may be part of wider rows), y float32 or bfloat16."""
+    """y[n, h, :] = o[n, h, :] * sigmoid(gate[n, h]); o float32 or bfloat16 [rows, heads * value_dim], gate float32
+    [rows, heads] (may be part of wider rows), y float32 or bfloat16."""
     pg, ldg = _rows_ld(gate, "gate")
     if tuple(y.shape) != tuple(o.shape) or o.shape[1] != heads * value_dim:
         raise Backend("head_scalar_gate: shapes disagree")
     _check(_fn("mixers", "esp_head_scalar_gate")(
-        _ptr(o, torch.float32, "o"), pg, ldg, _ptr(y, FLOATS, "y"), _is_bf16(y), o.shape[0], heads, value_dim, _stream()),
+        _ptr(o, FLOATS, "o"), _is_bf16(o), pg, ldg, _ptr(y, FLOATS, "y"), _is_bf16(y), o.shape[0], heads, value_dim, _stream()),
         "head_scalar_gate")
+
+
+def heads_to_pages(k, v, tok_seq, tok_pos, table, k_pool, v_pool, page, heads, key_dim, value_dim, status):
+    """Keys float32 [rows, heads * key_dim] and values float32 [rows, heads * value_dim] (may be parts of wider rows) into
+    the pools k_pool [pages, heads, page, key_dim] and v_pool [pages, heads, page, value_dim] at every token's place
+    (``table`` int32 [sequences, stride]: the pages of each sequence).  Sizes are multiples of four."""
+    (pk, ldk), (pv, ldv) = _rows_ld(k, "k"), _rows_ld(v, "v")
+    if k.shape[1] != heads * key_dim or v.shape[1] != heads * value_dim or k_pool.dtype != v_pool.dtype:
+        raise Backend("heads_to_pages: shapes disagree")
+    _check(_fn("mixers", "esp_heads_to_pages")(
+        pk, ldk, pv, ldv, _ptr(tok_seq, torch.int32), _ptr(tok_pos, torch.int32), _ptr(table, torch.int32), table.shape[1],
+        k_pool.shape[0], page, _ptr(k_pool, FLOATS, "k_pool"), _ptr(v_pool, FLOATS, "v_pool"), _is_bf16(k_pool), k.shape[0],
+        heads, key_dim, value_dim, _ptr(status, torch.int32), _stream()), "heads_to_pages")
 
 
 def pair_rope_unitnorm_kvwrite(qkv, bias, inv_freq, rot, eps, unit_norm, v_shared, blend_mode, blend, tok_seq, tok_pos, q_out,

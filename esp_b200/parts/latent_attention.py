@@ -8,8 +8,13 @@ from ..cache import KvLayout
 from ..cache.book import PAGE
 from ..csrc import ops
 from ..errors import Unsupported
+from .attention import scaled_tiles
 from .base import ParamSpec, Part, build, register
 from .linear import linear
+
+# a step of whole prompts takes the unfolded form when its longest prompt has at least this many tokens (the folded
+# form's cost grows with rank x tokens squared: 2,048 tokens at rank 512 took 495 us against about 100 unfolded)
+UNFOLD_ROWS = 512
 
 
 class LatentAttention(Part):
@@ -20,7 +25,13 @@ class LatentAttention(Part):
     The cache holds one row [c | k_rot] per position and nothing per head.  The keys' up-projection is
     folded into the query (q_lat = W_uk^T q_nope per head) and the values' up-projection is applied to the
     weighted sum of latents, so every head attends to the cached rows themselves.  A layer without a
-    down-projection of its own (``own_kv`` False) reads the rows another layer cached, with its own window."""
+    down-projection of its own (``own_kv`` False) reads the rows another layer cached, with its own window.
+
+    A step that brings whole prompts (nothing cached before) of which one is long may take the unfolded form instead,
+    where the sizes allow it (bfloat16, no rotated part, no window, keys and values of one size that the tensor-memory
+    attention takes): every head's keys and values are made from the step's latents with one dense product, written
+    to pages of their own, and the tensor-memory attention of the other attention parts runs over them; the folded
+    form pays rank multiply-adds a score where this pays the head size.  The cache still gets the latents."""
 
     graph_safe = True
 
@@ -37,6 +48,7 @@ class LatentAttention(Part):
         if spec.kv_rank > 512:
             raise Unsupported("kv_rank", f"{spec.kv_rank}; the latent attention kernels take up to 512 value channels a row")
         self.w_q = None                          # full-rank queries (q_rank None): [queries; head gates] x hidden
+        self.w_ukv = None                        # [keys of every head; values of every head] x rank, for the unfolded form
         self.row = spec.kv_rank + spec.rot_dim
         self.q_head = spec.nope_dim + spec.rot_dim
         self.w_dq = self.dq_norm = self.w_uq = self.w_dkv = self.dkv_norm = self.w_uk = self.w_uv = self.w_o = self.w_gate = None
@@ -98,6 +110,8 @@ class LatentAttention(Part):
 
     def finalize(self):
         s = self.spec
+        if self.w_uk is not None and self.w_ukv is None and self._unfolded_fits():
+            self.w_ukv = torch.cat([self.w_uk, self.w_uv]).contiguous()
         if self.w_uk is not None and self.w_uk_t is None:
             # per head [kv_rank, nope]: the product that folds the keys' up-projection into the query reads it row by row
             self.w_uk_t = self.w_uk.view(s.num_heads, s.nope_dim, s.kv_rank).transpose(1, 2).contiguous()
@@ -115,17 +129,39 @@ class LatentAttention(Part):
     def _tensor_cores(self, page: int = PAGE) -> bool:
         return self.rt.dtype == torch.bfloat16 and ops.attn_latent_mma_fits(self.row, self.spec.kv_rank, page)
 
+    def _unfolded_fits(self) -> bool:
+        s = self.spec
+        return (self.rt.dtype == torch.bfloat16 and s.own_kv and s.rot_dim == 0 and s.window is None and s.scale > 0
+                and s.nope_dim == s.value_dim and ops.attn_prefill_tc05_fits(s.nope_dim, PAGE) and s.kv_rank % 8 == 0
+                and self.w_uk is not None and self.w_uk.dtype == torch.bfloat16 and self.w_uv.dtype == torch.bfloat16)
+
     def step_arrays_key(self):
-        return ("latent_attention", self.rt.dtype, ops.attn_latent_mma_heads(self.spec.num_heads)) if self._tensor_cores() else None
+        if not self._tensor_cores() and self.w_ukv is None:
+            return None
+        return ("latent_attention", self.rt.dtype, ops.attn_latent_mma_heads(self.spec.num_heads), self._tensor_cores(),
+                self.w_ukv is not None)
 
     def step_arrays(self, step):
-        """Tiles of new tokens of one sequence for the tensor-core kernel: (sequence, first new token) per tile."""
-        if not self._tensor_cores():
-            return {}
-        tq = ops.ATTN_LATENT_MMA_ROWS // ops.attn_latent_mma_heads(self.spec.num_heads)
-        tiles = [(i, f) for i, t in enumerate(step.news) for f in range(0, t, tq)]
-        return {f"latent.tiles{tq}.seq": np.asarray([t[0] for t in tiles], dtype=np.int32),
-                f"latent.tiles{tq}.first": np.asarray([t[1] for t in tiles], dtype=np.int32)}
+        """Tiles of new tokens of one sequence for the tensor-core kernel: (sequence, first new token) per tile.  For a
+        step of whole prompts with a long one, where the unfolded form runs: the pages of the step's own keys and
+        values (sequence after sequence) and the tiles of the tensor-memory attention."""
+        out = {}
+        if self.w_ukv is not None and max(step.news) >= UNFOLD_ROWS and not any(step.pasts):
+            pages = [(t + PAGE - 1) // PAGE for t in step.news]
+            table = np.full((len(pages), max(pages)), -1, dtype=np.int32)
+            at = 0
+            for i, n in enumerate(pages):
+                table[i, :n] = np.arange(at, at + n, dtype=np.int32)
+                at += n
+            out["latent.unfolded.table"] = table
+            out.update(scaled_tiles("tc05", step))
+            return out
+        if self._tensor_cores():
+            tq = ops.ATTN_LATENT_MMA_ROWS // ops.attn_latent_mma_heads(self.spec.num_heads)
+            tiles = [(i, f) for i, t in enumerate(step.news) for f in range(0, t, tq)]
+            out[f"latent.tiles{tq}.seq"] = np.asarray([t[0] for t in tiles], dtype=np.int32)
+            out[f"latent.tiles{tq}.first"] = np.asarray([t[1] for t in tiles], dtype=np.int32)
+        return out
 
     def attend(self, qx, o_lat, ctx, layer, table):
         s, rt = self.spec, self.rt
@@ -155,6 +191,34 @@ class LatentAttention(Part):
             part_ml = rt.ws.get("la_part_ml", (n, H, n_splits, 2), torch.float32)
         ops.attn_latent_mma(qx, layer.k, o_lat, tile_seq, tile_first, ctx.seq_start, ctx.seq_past, table, layer.page, H, self.row,
                             s.kv_rank, s.window, s.scale, rt.status, n_splits, per, part_o, part_ml)
+
+    def _attend_unfolded(self, q, d, gate, ctx, table):
+        """Whole prompts: keys and values of every head from the step's own latents, then the tensor-memory attention.
+        q float32 [n, H * K] (a view), d float32 [n, rank] the down-projection's output, gate float32 [n, H] or None."""
+        s, rt = self.spec, self.rt
+        n, H, K = q.shape[0], s.num_heads, s.nope_dim
+        c = rt.ws.get("la_c_act", (n, s.kv_rank), rt.dtype)
+        ops.add_rmsnorm(d, None, self.dkv_norm, c, s.eps, write_x=False)          # the rows the cache got, as a matrix
+        kv = rt.ws.get("la_kv", (n, 2 * H * K), torch.float32)
+        linear(rt, c, self.w_ukv, kv)
+        n_pages = int(table.shape[0]) * int(table.shape[1])
+        k_pool = rt.ws.get("la_k_pages", (n_pages, H, PAGE, K), rt.dtype)
+        v_pool = rt.ws.get("la_v_pages", (n_pages, H, PAGE, K), rt.dtype)
+        # what lies behind a prompt's last token in its last page is masked, but a weight of zero times a value that is
+        # no number is no number: the pages start from zeros, as the cache's own pools do
+        k_pool.zero_()
+        v_pool.zero_()
+        ops.heads_to_pages(kv[:, :H * K], kv[:, H * K:], ctx.tok_seq, ctx.tok_pos, table, k_pool, v_pool, PAGE, H, K, K, rt.status)
+        qa = rt.ws.get("la_q_act", (n, H * K), rt.dtype)
+        ops.cast_cols(q, qa)
+        o = rt.ws.get("la_o", (n, H * K), rt.dtype)
+        rows = ops.ATTN_TC05_TILE_ROWS
+        ops.attn_prefill_tc05(qa, k_pool, v_pool, o, ctx.arrays[f"attention.tiles{rows}.seq"],
+                              ctx.arrays[f"attention.tiles{rows}.first"], ctx.seq_start, ctx.seq_past, table, PAGE, H, H, K,
+                              None, rt.status, scale=s.scale)
+        if gate is not None:
+            ops.head_scalar_gate(o, gate, o, H, K)
+        return o
 
     def forward(self, h, ctx, layer):
         s, rt, pos = self.spec, self.rt, self.position
@@ -186,6 +250,12 @@ class LatentAttention(Part):
             linear(rt, h, self.w_dkv, d)
             ops.latent_kv_store(d, self.dkv_norm, inv_freq, magnitude, rot_dims, ctx.tok_seq, ctx.tok_pos,
                                 table, layer.k, layer.page, s.kv_rank, s.rot_dim, s.eps, rt.status)
+        unfolded = ctx.arrays.get("latent.unfolded.table") if (self.w_ukv is not None and layer.writes) else None
+        if unfolded is not None:
+            o = self._attend_unfolded(q, d, gate, ctx, unfolded)
+            y = rt.ws.get("mixer_out", (n, s.hidden), torch.float32)
+            linear(rt, o, self.w_o, y)
+            return y
         qx = rt.ws.get("la_qx", (n, H * self.row), rt.dtype)
         if s.rot_dim:
             ops.latent_q_rotate(q, inv_freq, magnitude, rot_dims, ctx.tok_pos, qx, H, s.nope_dim, s.rot_dim, s.kv_rank)

@@ -247,6 +247,47 @@ def test_cuttings_agree_bit_for_bit_in_float32(folders, name):
             assert np.array_equal(first, other.logits_of(rid, at))
 
 
+@pytest.mark.parametrize("heads, dim, rank", [(3, 64, 48), (2, 128, 32)])
+def test_whole_long_prompts_take_the_unfolded_latent_attention(tmp_path, heads, dim, rank):
+    """A step of whole prompts of which one has 600 tokens, in bfloat16 at head sizes 64 and 128: every head's keys and
+    values are made from the step's latents and the tensor-memory attention runs over them; the tokens decoded afterwards
+    read the latents that the same step cached.  The same requests in portions (the folded form) agree within the bound."""
+    from esp_b200.csrc import ops
+    raw = {"architecture": "Sebevik", "vocab": 91, "width": 64, "norm": {"eps": 1e-5}, "layers": [
+        {"type": "latent_attention", "mixer": {"heads": heads, "dim": dim, "vdim": dim, "kv_rank": rank, "scale": 0.11},
+         "mlp": {"kind": "dense", "ff": 48}},
+        {"type": "latent_attention", "mixer": {"heads": 2, "dim": 24, "vdim": 24, "kv_rank": 32, "scale": 0.2}, "mlp": None}]}
+    w = plain.random_weights(raw, 11)
+    (tmp_path / "config.json").write_text(json.dumps(raw))
+    write_safetensors(tmp_path / "model.safetensors", w)
+    rng = np.random.default_rng(4)
+    reqs = {f"r{i}": [int(t) for t in rng.integers(0, raw["vocab"], n)] for i, n in enumerate((620, 75, 130))}
+    eng = Engine.from_folder(tmp_path, dtype="bfloat16", max_tokens=2048)
+    # scratch that held values that are no numbers: what lies behind a prompt's end in its last page must not count
+    for name in ("la_k_pages", "la_v_pages"):
+        eng.rt.ws.get(name, (64, heads, 64, dim), torch.bfloat16).fill_(float("nan"))
+    calls = []
+    real = ops.heads_to_pages
+    ops.heads_to_pages = lambda *a, **k: (calls.append(1), real(*a, **k))[1]
+    try:
+        ids = list(reqs)
+        rec = Recorder(raw["vocab"])
+        run_steps(eng, steps_batches(reqs, [ids], {rid: len(t) - 12 for rid, t in reqs.items()}), rec)
+        assert len(calls) == 1                  # the first layer, in the step of the prompts; the second one's sizes do not fit
+        rec2 = Recorder(raw["vocab"])
+        run_steps(eng, steps_portions(reqs, [300, 7, 64]), rec2)
+        assert len(calls) == 1
+    finally:
+        ops.heads_to_pages = real
+    for rid, toks in reqs.items():
+        ref = plain.forward(raw, w, toks).numpy()
+        for r in (rec, rec2):
+            d = r.logits_of(rid, list(range(len(toks)))) - ref
+            d = d - d.mean(1, keepdims=True)
+            err = np.sqrt((d ** 2).mean(1)) / np.sqrt((ref ** 2).mean())
+            assert err.max() <= BOUND["bfloat16"], (rid, int(err.argmax()), float(err.max()))
+
+
 def test_long_decoding_in_a_small_cache(folders):
     """300 single tokens after a prompt of 3 in a cache of 6 pages: the windowed layers give their old pages back and
     get them again, the layer that sees everything keeps its five, the recurrent state carries the rest."""

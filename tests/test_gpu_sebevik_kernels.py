@@ -425,3 +425,40 @@ def test_a_gate_per_head_scales_the_heads_whole_output():
         ops.head_scalar_gate(dev(o), wd[:, 9:], y, H, V)
         want = o.double().view(n, H, V) * plain.sigmoid(wide[:, 9:].double())[:, :, None]
         assert (y.double().cpu().view(n, H, V) - want).abs().max() < (1e-6 if dtype == torch.float32 else 2e-2)
+
+
+def test_the_gate_takes_rounded_input_in_place():
+    g = torch.Generator().manual_seed(3)
+    n, H, V = 21, 3, 64
+    o = torch.randn(n, H * V, generator=g).to(torch.bfloat16)
+    gate = torch.randn(n, H, generator=g)
+    y = dev(o)
+    ops.head_scalar_gate(y, dev(gate), y, H, V)
+    want = o.double().view(n, H, V) * plain.sigmoid(gate.double())[:, :, None]
+    assert (y.double().cpu().view(n, H, V) - want).abs().max() < 2e-2
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_keys_and_values_of_every_head_into_pages_of_their_own(dtype):
+    g = torch.Generator().manual_seed(5)
+    H, K = 3, 64
+    runs = [70, 1, 130]
+    rows = sum(runs)
+    kv = torch.randn(rows, 2 * H * K, generator=g)
+    table = torch.full((3, 3), -1, dtype=torch.int32)
+    table[0, :2] = torch.tensor([4, 1])
+    table[1, :1] = torch.tensor([0])
+    table[2, :3] = torch.tensor([5, 2, 3])
+    seq = sum(([i] * n for i, n in enumerate(runs)), [])
+    pos = sum((list(range(n)) for n in runs), [])
+    k_pool = torch.zeros(6, H, PAGE, K, dtype=dtype, device=DEV)
+    v_pool = torch.zeros(6, H, PAGE, K, dtype=dtype, device=DEV)
+    kvd = dev(kv)
+    st = status()
+    ops.heads_to_pages(kvd[:, :H * K], kvd[:, H * K:], i32(seq), i32(pos), dev(table), k_pool, v_pool, PAGE, H, K, K, st)
+    assert int(st.item()) == 0
+    for r in range(rows):
+        page = int(table[seq[r], pos[r] // PAGE])
+        assert torch.equal(k_pool[page, :, pos[r] % PAGE].cpu(), kv[r, :H * K].view(H, K).to(dtype))
+        assert torch.equal(v_pool[page, :, pos[r] % PAGE].cpu(), kv[r, H * K:].view(H, K).to(dtype))
+    assert int((k_pool != 0).any(-1).sum().item()) == rows * H
