@@ -338,7 +338,7 @@ def route_want(h, w_router, correction, top, groups, keep):
 
 @pytest.mark.parametrize("n, width, wdtype", [(5, 96, torch.float32), (40, 128, torch.bfloat16), (100, 96, torch.float32),
                                               (300, 256, torch.bfloat16), (70, 100, torch.bfloat16)])
-@pytest.mark.parametrize("outputs, real, top, groups, keep", [(16, 12, 3, 2, 1), (9, 7, 2, 3, 2), (6, 6, 6, 0, 0), (12, 5, 4, 4, 2),
+@pytest.mark.parametrize("outputs, real, top, groups, keep", [(18, 14, 4, 3, 1), (9, 7, 2, 3, 2), (6, 6, 6, 0, 0), (12, 5, 4, 4, 2),
                                                               (40, 33, 8, 1, 1)])
 def test_corrected_group_limited_choice_and_outputs_without_an_expert(n, width, wdtype, outputs, real, top, groups, keep):
     """Every path of the router (two launches for few tokens; a block per few tokens; logits on the tensor cores for many

@@ -34,7 +34,7 @@ def draw(rng):
             if rng.integers(0, 5) > 0:
                 mixer["rot"] = {"dims": 2 * int(rng.integers(1, dim // 2 + 1)), "base": pick(50.0, 1000.0, 10000.0, 500000.0)}
             if rng.integers(0, 6) > 0:
-                mixer["mask"] = {"size": pick(1, 3, 17, 40, 63, 64, 65, 100, 128, 500)}
+                mixer["mask"] = {"size": pick(1, 3, 17, 41, 63, 64, 65, 100, 128, 500)}
             if rng.integers(0, 2):
                 if blend is None:
                     blend = (mixer["kv_heads"], mixer["vdim"])
