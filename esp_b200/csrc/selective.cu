@@ -43,6 +43,30 @@ __device__ __forceinline__ float sel_exp2(float v) {
     return r;
 }
 
+// 2^v for v <= 0 from multiply-adds alone, to within about one unit in the last place: v = n + f with n whole and
+// |f| <= 1/2, 2^f by the series of exp(f ln 2) up to the seventh power (the next term is below 5e-9), the exponent
+// added to the result's.  The special-function unit's 2^v is off by up to 2^-22.5, and by the same amount whenever the
+// argument is the same: a state entry that keeps most of itself for hundreds of tokens multiplies as many such factors,
+// and their errors add up instead of averaging out (the 32-bit engine's residual stream behind a scan of 1,100 tokens was
+// 2.6 times as far from a 64-bit run as a plain 32-bit implementation's).  The 32-bit engine takes this form.
+__device__ __forceinline__ float sel_exp2_series(float v) {
+    v = fmaxf(v, -126.0f);                       // below that the result leaves the normal range: it is nothing either way
+    const float n = rintf(v);
+    const float f = v - n;                       // exact
+    float p = 1.525273380405984e-05f;
+    p = fmaf(p, f, 1.5403530393381608e-04f);
+    p = fmaf(p, f, 1.3333558146428443e-03f);
+    p = fmaf(p, f, 9.618129107628477e-03f);
+    p = fmaf(p, f, 5.550410866482158e-02f);
+    p = fmaf(p, f, 2.402265069591007e-01f);
+    p = fmaf(p, f, 6.931471805599453e-01f);
+    p = fmaf(p, f, 1.0f);
+    return __int_as_float(__float_as_int(p) + ((int)n << 23));
+}
+template <typename TY> __device__ __forceinline__ float sel_decay(float v);
+template <> __device__ __forceinline__ float sel_decay<float>(float v) { return sel_exp2_series(v); }
+template <> __device__ __forceinline__ float sel_decay<bf16>(float v) { return sel_exp2(v); }
+
 __device__ __forceinline__ float sel_softplus(float v) { return v > 20.f ? v : log1pf(expf(v)); }
 
 // grid (channel tiles, sequences); block SEL_THREADS = cpb channels x L lanes a channel
@@ -147,7 +171,7 @@ selective_scan_kernel(const float* __restrict__ x, long long ldx, const float* _
             for (int u = 0; u < SEL_GROUP; u++) {
                 const float dt = t0 + u < count ? per[(t0 + u) * cpb + ch_local] : 0.f;
 #pragma unroll
-                for (int j = 0; j < SLICE; j++) decay[u][j] = sel_exp2(dt * A2[j]);
+                for (int j = 0; j < SLICE; j++) decay[u][j] = sel_decay<TY>(dt * A2[j]);
             }
             float acc[SEL_GROUP];
 #pragma unroll

@@ -276,11 +276,13 @@ def test_selective_scan_over_unequal_runs_from_and_to_the_state(C, N):
     assert torch.equal(y, y2)
     for s in slots:
         assert torch.equal(state[s, :C * N], state2[s, :C * N])
-    # bfloat16 output: the same values, rounded once
+    # bfloat16 output (the bfloat16 engine's form: its exponentials come from the special-function unit, the 32-bit
+    # engine's from multiply-adds): the same values up to that and one rounding
     y16 = torch.zeros(rows, C, device=DEV, dtype=torch.bfloat16)
     ops.selective_scan(wide[:, :C], dev(dt_raw), low[:, 5:], wide[:, C + 3:], dev(a_log), dev(skip), torch.zeros_like(state), starts,
                        i32(slots), y16, len(runs), C, N)
-    assert torch.equal(y16, y.to(torch.bfloat16))
+    assert ((y16.float() - y).abs() <= 2.0 ** -7 * y.abs() + 1e-4 * float(y.abs().max())).all()
+    assert (y16.double().cpu() - want).abs().max() < 1e-2 * max(1.0, float(want.abs().max()))
 
 
 def test_selective_scan_keeps_what_it_wrote_for_hundreds_of_tokens():
